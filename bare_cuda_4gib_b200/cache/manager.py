@@ -4,7 +4,8 @@ with the same needs, and slots of fixed-size per-request state beside them.
 * A *cache* belongs to one run of a layer (an entry of the model's run order).  Caches whose
   mixers ask for the same thing (`KVCacheRequest`: kv heads, head size, window) form a *group*.
   A group has a page pool and storage of its own; one page holds `page_tokens` positions of
-  every cache of the group: [cache][keys | values][kv head][token in page][head_dim].
+  every cache of the group: [cache][keys | values][kv head][token in page][head_dim] (values with
+  their own head size where a mixer asks for one).
   (cuongvng/bare-cuda-4gib has one group: a page holds K for every layer then V for every
   layer, 64 tokens: engine/include/llm/kv_cache.h:14-32.)
 * A request owns a *slot*; per group the slot has a block table: the page of its n-th block of
@@ -56,7 +57,8 @@ class CacheGroup:
         self.pool = PagePool(num_pages)
         self.tables: Dict[int, List[int]] = {}      # slot -> page per block (-1 = none)
         self.dtype = dtype
-        self.cache_elems = 2 * request.kv_heads * page_tokens * request.head_dim
+        self.key_elems = request.kv_heads * page_tokens * request.head_dim      # values follow the keys
+        self.cache_elems = self.key_elems + request.kv_heads * page_tokens * request.value_dim
         self.page_stride = len(members) * self.cache_elems
         self.storage = None
         if allocate:
@@ -258,9 +260,10 @@ class CacheManager:
             return None
         esize = g.storage.element_size()
         k_ptr = g.storage.data_ptr() + j * g.cache_elems * esize
-        v_ptr = k_ptr + (g.cache_elems // 2) * esize
+        v_ptr = k_ptr + g.key_elems * esize
         return CacheView(k_ptr, v_ptr, block_table, g.page_stride, block_table.stride(0), g.page_tokens,
-                         g.request.kv_heads, g.request.head_dim, g.dtype, g.storage.data_ptr(), g.storage.numel())
+                         g.request.kv_heads, g.request.head_dim, g.dtype, g.storage.data_ptr(), g.storage.numel(),
+                         v_dim=g.request.value_dim)
 
     # ------------------------------------------------------------------ accounting
     def pages_in_use(self) -> List[int]:

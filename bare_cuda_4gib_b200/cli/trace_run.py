@@ -32,7 +32,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (rounded up per request to a page)")
     ap.add_argument("--page-tokens", type=int, default=64, help="positions per cache page (default 64)")
-    ap.add_argument("--max-live", type=int, default=8, help="request slots (default 8)")
+    ap.add_argument("--max-live", type=int, default=4, help="request slots: the most requests live at a time (default 4)")
     args = ap.parse_args(argv)
 
     import torch

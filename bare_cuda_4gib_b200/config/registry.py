@@ -34,8 +34,11 @@ def registered_architectures():
 
 def resolve_architecture(config_dict: Dict[str, Any]) -> Architecture:
     names = config_dict.get("architectures")
+    if names is None and isinstance(config_dict.get("architecture"), str):
+        names = [config_dict["architecture"]]          # some layouts name one class as a plain string
     if not names or not isinstance(names, (list, tuple)) or not isinstance(names[0], str):
-        raise ConfigError("config.json: 'architectures' must be a list that names the model class")
+        raise ConfigError("config.json: 'architectures' must be a list that names the model class "
+                          "(or 'architecture' its name)")
     if names[0] not in _ARCHITECTURES:
         raise ConfigError(f"config.json: architecture '{names[0]}' is not registered "
                           f"(registered: {registered_architectures()})")

@@ -42,11 +42,17 @@ from .spec import PartSpec, WeightSpec
 @dataclass(frozen=True)
 class KVCacheRequest:
     """Keys and values per token that a mixer wants paged: `window` None keeps every key, a
-    number keeps the last `window` positions (older pages are given back)."""
+    number keeps the last `window` positions (older pages are given back).  `v_head_dim` is the
+    size of a value head where it differs from the key head's `head_dim`."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else int(self.v_head_dim)
 
 
 @dataclass(frozen=True)

@@ -44,3 +44,28 @@ class OutputHead(Part):
 
     def forward(self, ctx, normed, rows: int) -> torch.Tensor:
         return self.linear.forward(ctx, normed, rows, torch.float32, "logits").tensor
+
+
+@register_embedding("table_positions")
+class ScaledPositionEmbedding(Part):
+    """x = E[id] * scale + P[position] (P a learned table, not scaled), in float32, written into
+    every one of `streams` copies of the residual: the result is [tokens, streams * hidden].
+
+    params: `vocab`, `hidden`, `scale`, `positions` (rows of the position table, or None for no
+    position term), `streams`.  tensors: `weight` [vocab, hidden], `positions` [positions, hidden]."""
+
+    def local_weights(self):
+        p = self.params
+        out = {"weight": ((int(p["vocab"]), int(p["hidden"])), "matrix")}
+        if p.get("positions"):
+            out["positions"] = ((int(p["positions"]), int(p["hidden"])), "matrix")
+        return out
+
+    def forward(self, ctx) -> torch.Tensor:
+        from ..kernels import streams as SK
+        p = self.params
+        width, streams = int(p["hidden"]), int(p.get("streams") or 1)
+        x = ctx.ws.get("streams", (ctx.n_tokens, streams * width), torch.float32)
+        SK.embed_positions(self.tensors["weight"], self.tensors.get("positions"), ctx.token_ids, ctx.positions, x,
+                           ctx.n_tokens, width, streams, float(p.get("scale", 1.0)), ctx.stream)
+        return x

@@ -41,3 +41,35 @@ class SwiGLUFeedForward(Part):
         residual = getattr(ctx, "residual", None)
         return self.down.forward(ctx, act.tensor, n, torch.float32, "ffn_out", allow_partials=True,
                                  epilogue=K.AddTo(residual, getattr(ctx, "following_norm", None)) if residual is not None else None)
+
+
+@register_feed_forward("dense")
+class DenseFeedForward(Part):
+    """down(act(up(h))), no gate and no biases; `activation` is "relu2" (the square of relu),
+    "gelu_tanh", "silu" or "relu".
+
+    params: `hidden`, `intermediate`, `activation`.  tensors: `up`, `down`."""
+
+    takes_lazy_input = False
+
+    def local_weights(self):
+        h, i = int(self.params["hidden"]), int(self.params["intermediate"])
+        return {"up": ((i, h), "matrix"), "down": ((h, i), "matrix")}
+
+    def prepare(self, dtype, device) -> None:
+        from ..kernels.streams import ACTIVATIONS
+        if self.params.get("activation", "relu2") not in ACTIVATIONS:
+            raise KeyError(f"dense feed-forward: activation '{self.params.get('activation')}' is not one of {sorted(ACTIVATIONS)}")
+        t = self.tensors
+        self.up = Linear(t.pop("up"), "up")
+        self.down = Linear(t.pop("down"), "down")
+        self.up.prepare(dtype)
+        self.down.prepare(dtype)
+
+    def forward(self, ctx, h):
+        from ..kernels import streams as SK
+        n = ctx.n_tokens
+        z = self.up.forward(ctx, h, n, ctx.dtype, "ffn_up")
+        act = ctx.ws.get("ffn_act", (n, int(self.params["intermediate"])), ctx.dtype)
+        SK.activation(z, act, n, self.params.get("activation", "relu2"), ctx.stream)
+        return self.down.forward(ctx, act, n, torch.float32, "ffn_out", allow_partials=True)

@@ -25,13 +25,16 @@ class PartSpec:
 
 @dataclass
 class LayerSpec:
-    """One layer: an arrangement (`block`) of a mixer and a feed-forward with their norms."""
+    """One layer: an arrangement (`block`) of a mixer and a feed-forward with their norms.  A layer
+    without a feed-forward has None in both of its places; `extras` holds what else an arrangement
+    needs, by a name of its own choosing."""
 
     mixer_norm: PartSpec
     mixer: PartSpec
-    ffn_norm: PartSpec
-    ffn: PartSpec
+    ffn_norm: Optional[PartSpec]
+    ffn: Optional[PartSpec]
     block: str = "prenorm"
+    extras: Dict[str, PartSpec] = field(default_factory=dict)
 
 
 @dataclass
@@ -48,8 +51,9 @@ class WeightSpec:
     """A tensor a part expects in the weight file."""
 
     name: str                 # name in the file
-    shape: Tuple[int, ...]
-    init: str = "matrix"      # random-weights mode: "matrix" ~ N(0, 0.02); "norm" ~ 1 + N(0, 0.01)
+    shape: Tuple[int, ...]    # an extent of -1 is taken from the file (random weights need every extent)
+    init: str = "matrix"      # random-weights mode: "matrix" ~ N(0, 0.02); "norm" ~ 1 + N(0, 0.01);
+                              # "identity" ~ I + N(0, 0.01); "unit" ~ N(0, 1)
     integer: bool = False     # integer tables are kept as int32
 
 

@@ -54,7 +54,8 @@ def check_names_and_shapes(expected: Dict[str, WeightSpec], present: Dict[str, T
         if source is None or source not in present:
             missing.append(name)
             continue
-        if tuple(present[source]) != tuple(spec.shape):
+        have, need = tuple(present[source]), tuple(spec.shape)
+        if len(have) != len(need) or any(n >= 0 and n != h for h, n in zip(have, need)):     # -1: whatever the file has
             wrong.append(f"{name}: file has {list(present[source])}, the model needs {list(spec.shape)}")
         resolved[name] = source
     used = set(resolved.values())

@@ -32,9 +32,16 @@ def _generator(seed: int, name: str, device) -> torch.Generator:
 
 
 def random_tensor(spec: WeightSpec, seed: int, name: str, dtype: torch.dtype, device) -> torch.Tensor:
+    if any(int(n) < 0 for n in spec.shape):
+        raise ValueError(f"random weights: the shape of '{name}' {tuple(spec.shape)} leaves an extent to the file")
     g = _generator(seed, name, device)
     x = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
-    x = 1.0 + NORM_STD * x if spec.init == "norm" else MATRIX_STD * x
+    if spec.init == "norm":
+        x = 1.0 + NORM_STD * x
+    elif spec.init == "identity":
+        x = torch.eye(spec.shape[0], spec.shape[1], dtype=torch.float32, device=device) + NORM_STD * x
+    elif spec.init != "unit":
+        x = MATRIX_STD * x
     return x.to(dtype)
 
 

@@ -23,6 +23,13 @@
 // Softmax runs in base 2: scores are multiplied by scale * log2(e).
 //
 // HEAD_DIM is a compile-time constant (-DHEAD_DIM=64): a multiple of 16 up to 128.
+//
+// -DDISTANCE_BIAS builds the variant for attention with a learned bias by distance: the score of
+// (query at position i, key at position j, head h) is (q . k) * scale + bias[h][i - j], with
+// bias float32 [q_heads][bias_len].  In this variant the softmax weights enter the second product
+// as a sum of two bfloat16 numbers (the weight rounded, and what the rounding left), so a weight
+// keeps 16 significant bits instead of 8.  The output may be a column view of a wider matrix
+// (`out_stride`) and is multiplied by `out_scale`.
 
 #include "common.cuh"
 
@@ -96,6 +103,10 @@ struct AttnArgs {
   int q_heads;
   float scale_log2;
   int window;                  // <= 0: every key
+  long long out_stride;        // elements between output rows (q_heads * D when the output stands alone)
+  float out_scale;             // factor on the output
+  const float* bias;           // DISTANCE_BIAS: [q_heads][bias_len] by distance
+  int bias_len;
 };
 
 template <int WARPS_M, int WARPS_N, int MT>
@@ -216,6 +227,9 @@ attention_mma_kernel(AttnArgs a) {
 
   // this thread's rows: two per row tile
   int row_pos[MT][2];
+#ifdef DISTANCE_BIAS
+  const float* row_bias[MT][2];  // the bias row of this row's head
+#endif
   float m[MT][2], l[MT][2];
   float o[MT][D / 8][4];
 #pragma unroll
@@ -224,6 +238,9 @@ attention_mma_kernel(AttnArgs a) {
     for (int h = 0; h < 2; ++h) {
       const int R = row0 + wm * WR + mt * 16 + (lane >> 2) + h * 8;
       row_pos[mt][h] = R < n_rows ? pos0 + R / group : -1;  // -1: no key is visible
+#ifdef DISTANCE_BIAS
+      row_bias[mt][h] = a.bias + (long long)(kvh * group + R % group) * a.bias_len;
+#endif
       m[mt][h] = -INFINITY;
       l[mt][h] = 0.0f;
     }
@@ -261,7 +278,12 @@ attention_mma_kernel(AttnArgs a) {
     }
 
     // a block wholly below every row's position and inside every row's window needs no mask
+#ifdef DISTANCE_BIAS
+    const bool all_visible = false;   // every score gets its own bias: one path
+    uint32_t pf_lo[MT][NT / 2][4];
+#else
     const bool all_visible = kb * BN + BN - 1 <= tile_min_pos && (a.window <= 0 || kb * BN > tile_max_pos - a.window);
+#endif
     uint32_t pf[MT][NT / 2][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
@@ -285,7 +307,13 @@ attention_mma_kernel(AttnArgs a) {
             const int h = e >> 1;
             const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
             const bool visible = key <= row_pos[mt][h] && (a.window <= 0 || key > row_pos[mt][h] - a.window);
+#ifdef DISTANCE_BIAS
+            const float v = visible ? fmaf(s[mt][nt][e], a.scale_log2,
+                                           1.4426950408889634f * __ldg(row_bias[mt][h] + min(row_pos[mt][h] - key, a.bias_len - 1)))
+                                    : -INFINITY;
+#else
             const float v = visible ? s[mt][nt][e] * a.scale_log2 : -INFINITY;
+#endif
             s[mt][nt][e] = v;
             mx[h] = fmaxf(mx[h], v);
           }
@@ -321,6 +349,13 @@ attention_mma_kernel(AttnArgs a) {
         l[mt][1] += p2 + p3;
         pf[mt][nt / 2][(nt & 1) * 2 + 0] = pack_bf16(p0, p1);
         pf[mt][nt / 2][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+#ifdef DISTANCE_BIAS
+        // what the rounding to bfloat16 left of each weight
+        pf_lo[mt][nt / 2][(nt & 1) * 2 + 0] = pack_bf16(p0 - __bfloat162float(__float2bfloat16_rn(p0)),
+                                                        p1 - __bfloat162float(__float2bfloat16_rn(p1)));
+        pf_lo[mt][nt / 2][(nt & 1) * 2 + 1] = pack_bf16(p2 - __bfloat162float(__float2bfloat16_rn(p2)),
+                                                        p3 - __bfloat162float(__float2bfloat16_rn(p3)));
+#endif
       }
     }
 #pragma unroll
@@ -334,6 +369,10 @@ attention_mma_kernel(AttnArgs a) {
         for (int mt = 0; mt < MT; ++mt) {
           mma_bf16(o[mt][dt], pf[mt][kk], vf[0], vf[1]);
           mma_bf16(o[mt][dt + 1], pf[mt][kk], vf[2], vf[3]);
+#ifdef DISTANCE_BIAS
+          mma_bf16(o[mt][dt], pf_lo[mt][kk], vf[0], vf[1]);
+          mma_bf16(o[mt][dt + 1], pf_lo[mt][kk], vf[2], vf[3]);
+#endif
         }
       }
     }
@@ -387,7 +426,7 @@ attention_mma_kernel(AttnArgs a) {
         for (int e = 0; e < 8; ++e) acc[e] += src[e] * f;
       }
     }
-    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    const float inv = L > 0.0f ? (n_splits == 1 ? a.out_scale : 1.0f) / L : 0.0f;
     if (n_splits == 1) {
       if (R < n_rows) {
         const int token = R / group, head = kvh * group + R % group;
@@ -396,7 +435,7 @@ attention_mma_kernel(AttnArgs a) {
         packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
         packed.z = pack_bf16(acc[4] * inv, acc[5] * inv);
         packed.w = pack_bf16(acc[6] * inv, acc[7] * inv);
-        *reinterpret_cast<uint4*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D + c * 8) = packed;
+        *reinterpret_cast<uint4*>(a.out + (long long)(q_start + token) * a.out_stride + head * D + c * 8) = packed;
       }
     } else {
       float* dst = a.part_o + (item * BM + r) * D + c * 8;
@@ -445,14 +484,14 @@ attention_mma_kernel(AttnArgs a) {
         acc[4] += w * hi.x; acc[5] += w * hi.y; acc[6] += w * hi.z; acc[7] += w * hi.w;
       }
     }
-    const float inv = W > 0.0f ? 1.0f / W : 0.0f;
+    const float inv = W > 0.0f ? a.out_scale / W : 0.0f;
     const int token = R / group, head = kvh * group + R % group;
     uint4 packed;
     packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
     packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
     packed.z = pack_bf16(acc[4] * inv, acc[5] * inv);
     packed.w = pack_bf16(acc[6] * inv, acc[7] * inv);
-    *reinterpret_cast<uint4*>(a.out + ((long long)(q_start + token) * a.q_heads + head) * D + c * 8) = packed;
+    *reinterpret_cast<uint4*>(a.out + (long long)(q_start + token) * a.out_stride + head * D + c * 8) = packed;
   }
   if (threadIdx.x == 0) *counter = 0;
 }
@@ -502,13 +541,15 @@ extern "C" long long llm_attention_scratch_floats(int n_tiles, int kv_heads, int
 
 // rows_per_tile: llm_attention_prefill_rows() (prefill shape) or 16 (decode shape).  `scratch` (llm_attention_scratch_floats
 // words, its first LLM_ATTENTION_COUNTER_WORDS zero) is needed when n_splits > 1.
-extern "C" int llm_attention_mma(const void* q, void* out, void* k_base, void* v_base, const int32_t* block_table,
-                                 long long page_stride, int table_stride, int page_tokens, int kv_heads,
-                                 int head_dim, const int32_t* seq_q_start, const int32_t* seq_q_len,
-                                 const int32_t* seq_kv_len, const int32_t* tile_seq, const int32_t* tile_index,
-                                 int n_tiles, int rows_per_tile, int n_splits, float* scratch, int q_heads,
-                                 float scale, int window, cudaStream_t stream) {
+static int attention_mma_launch(const void* q, void* out, long long out_stride, float out_scale, const float* bias,
+                                int bias_len, void* k_base, void* v_base, const int32_t* block_table,
+                                long long page_stride, int table_stride, int page_tokens, int kv_heads,
+                                int head_dim, const int32_t* seq_q_start, const int32_t* seq_q_len,
+                                const int32_t* seq_kv_len, const int32_t* tile_seq, const int32_t* tile_index,
+                                int n_tiles, int rows_per_tile, int n_splits, float* scratch, int q_heads,
+                                float scale, int window, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (out_stride % 8) return ERR_BAD_ALIGN;
   if (head_dim != D || q_heads % kv_heads || n_splits < 1 || n_splits > 65535 || kv_heads > 65535) return ERR_BAD_SIZE;
   if (n_splits > 1 && !scratch) return ERR_BAD_SIZE;
   if (n_splits > 1 && (long long)n_tiles * kv_heads > LLM_ATTENTION_COUNTER_WORDS) return ERR_BAD_SIZE;
@@ -530,10 +571,48 @@ extern "C" int llm_attention_mma(const void* q, void* out, void* k_base, void* v
   a.q_heads = q_heads;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;
+  a.out_stride = out_stride;
+  a.out_scale = out_scale;
+  a.bias = bias;
+  a.bias_len = bias_len;
   if (rows_per_tile == 64 * PREFILL_MT) return launch<4, 1, PREFILL_MT>(a, n_tiles, kv_heads, n_splits, stream);
   if (rows_per_tile == 16) return launch<1, 4, 1>(a, n_tiles, kv_heads, n_splits, stream);
   return ERR_BAD_SIZE;
 }
+
+extern "C" int llm_attention_mma(const void* q, void* out, void* k_base, void* v_base, const int32_t* block_table,
+                                 long long page_stride, int table_stride, int page_tokens, int kv_heads,
+                                 int head_dim, const int32_t* seq_q_start, const int32_t* seq_q_len,
+                                 const int32_t* seq_kv_len, const int32_t* tile_seq, const int32_t* tile_index,
+                                 int n_tiles, int rows_per_tile, int n_splits, float* scratch, int q_heads,
+                                 float scale, int window, cudaStream_t stream) {
+#ifdef DISTANCE_BIAS
+  return ERR_BAD_SIZE;   // this library is the variant with a bias: llm_attention_mma_bias
+#else
+  return attention_mma_launch(q, out, (long long)q_heads * D, 1.0f, nullptr, 0, k_base, v_base, block_table, page_stride,
+                              table_stride, page_tokens, kv_heads, head_dim, seq_q_start, seq_q_len, seq_kv_len,
+                              tile_seq, tile_index, n_tiles, rows_per_tile, n_splits, scratch, q_heads, scale, window,
+                              stream);
+#endif
+}
+
+#ifdef DISTANCE_BIAS
+// The variant with a bias by distance: `bias` float32 [q_heads][bias_len], `out` rows `out_stride`
+// elements apart, the output multiplied by `out_scale`.
+extern "C" int llm_attention_mma_bias(const void* q, void* out, long long out_stride, float out_scale,
+                                      const float* bias, int bias_len, void* k_base, void* v_base,
+                                      const int32_t* block_table, long long page_stride, int table_stride,
+                                      int page_tokens, int kv_heads, int head_dim, const int32_t* seq_q_start,
+                                      const int32_t* seq_q_len, const int32_t* seq_kv_len, const int32_t* tile_seq,
+                                      const int32_t* tile_index, int n_tiles, int rows_per_tile, int n_splits,
+                                      float* scratch, int q_heads, float scale, int window, cudaStream_t stream) {
+  if (!bias || bias_len < 1) return ERR_BAD_SIZE;
+  return attention_mma_launch(q, out, out_stride, out_scale, bias, bias_len, k_base, v_base, block_table, page_stride,
+                              table_stride, page_tokens, kv_heads, head_dim, seq_q_start, seq_q_len, seq_kv_len,
+                              tile_seq, tile_index, n_tiles, rows_per_tile, n_splits, scratch, q_heads, scale, window,
+                              stream);
+}
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // Entry point that allocates nothing (declared in attention_no_alloc.h; it has no counterpart in

@@ -36,17 +36,24 @@ def defines(head_dim: int):
     return (f"-DHEAD_DIM={head_dim}",)
 
 
-def lib(head_dim: int):
-    l = _libs.get(head_dim)
+def lib(head_dim: int, distance_bias: bool = False):
+    """The mma.sync kernel's library for this head size; with `distance_bias` the variant that adds
+    a bias by distance to every score (entry point `llm_attention_mma_bias`)."""
+    key = (head_dim, "bias") if distance_bias else head_dim
+    l = _libs.get(key)
     if l is None:
-        l = build.load_library("attention_mma.cu", defines(head_dim))
+        l = build.load_library("attention_mma.cu", defines(head_dim) + (("-DDISTANCE_BIAS",) if distance_bias else ()))
         P, I, L, F = c_void_p, c_int, c_longlong, c_float
         l.llm_attention_mma.argtypes = [P, P, P, P, P, L, I, I, I, I, P, P, P, P, P, I, I, I, P, I, F, I, P]
         l.llm_attention_mma.restype = c_int
+        if distance_bias:
+            l.llm_attention_mma_bias.argtypes = [P, P, L, F, P, I, P, P, P, L, I, I, I, I, P, P, P, P, P, I, I, I, P, I,
+                                                 F, I, P]
+            l.llm_attention_mma_bias.restype = c_int
         l.llm_attention_scratch_floats.argtypes = [I, I, I, I]
         l.llm_attention_scratch_floats.restype = c_longlong
         l.llm_attention_prefill_rows.restype = c_int
-        _libs[head_dim] = l
+        _libs[key] = l
     return l
 
 
@@ -82,17 +89,20 @@ def decode_lib(head_dim: int):
 
 
 class AttentionPlan:
-    def __init__(self, head_dim: int, heads: int, kv_heads: int):
+    def __init__(self, head_dim: int, heads: int, kv_heads: int, distance_bias: bool = False):
+        """`distance_bias`: attention whose scores get a bias by distance; only the mma.sync kernel
+        has that variant, so the plan uses it for every step shape."""
         self.head_dim, self.heads, self.kv_heads = head_dim, heads, kv_heads
         self.group = heads // kv_heads
-        self.lib = lib(head_dim)
+        self.distance_bias = distance_bias
+        self.lib = lib(head_dim, distance_bias)
         self.prefill_rows = int(self.lib.llm_attention_prefill_rows())
         self.tc = None
-        if head_dim in TC_HEAD_DIMS:
+        if head_dim in TC_HEAD_DIMS and not distance_bias:
             self.tc = tc_lib(head_dim)
             self.prefill_rows = int(self.tc.llm_attention_tc_rows())
         self.decode = None
-        if head_dim in TC_HEAD_DIMS and not os.environ.get("BARE_CUDA_B200_NO_DECODE_ATTENTION"):
+        if head_dim in TC_HEAD_DIMS and not distance_bias and not os.environ.get("BARE_CUDA_B200_NO_DECODE_ATTENTION"):
             self.decode = decode_lib(head_dim)
         self._host = None
         self._dev = None
@@ -161,15 +171,15 @@ class AttentionPlan:
         return self._scratch
 
 
-def plan_for(head_dim: int, heads: int, kv_heads: int) -> Optional[AttentionPlan]:
+def plan_for(head_dim: int, heads: int, kv_heads: int, distance_bias: bool = False) -> Optional[AttentionPlan]:
     if not supports(head_dim):
         return None
-    return AttentionPlan(head_dim, heads, kv_heads)
+    return AttentionPlan(head_dim, heads, kv_heads, distance_bias)
 
 
 def step_tiles(ctx, plan: AttentionPlan):
     """The step's row tiles for this head grouping: built once per step and shared by all layers."""
-    key = ("attention_tiles", plan.group, plan.kv_heads, plan.head_dim)
+    key = ("attention_tiles", plan.group, plan.kv_heads, plan.head_dim, plan.distance_bias)
     cached = ctx.extras.get(key)
     if cached is not None:
         return cached
@@ -218,9 +228,29 @@ def step_tiles(ctx, plan: AttentionPlan):
     return out
 
 
+def usable_with_bias(out: torch.Tensor, cache: CacheView) -> bool:
+    """Whether the variant with a bias can write `out` (possibly a column view) from this cache."""
+    return (out.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and cache.v_dim == cache.head_dim
+            and out.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 and out.stride(1) == 1)
+
+
 def run(ctx, plan: AttentionPlan, q: torch.Tensor, out: torch.Tensor, cache: CacheView, scale: float,
-        window: int) -> None:
+        window: int, bias: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
+    """`bias` (float32 [heads, distances], plans made with `distance_bias` only) is added to the
+    scaled scores by distance; such a plan may write a column view and scales its output."""
     tile_seq, tile_index, n_tiles, rows_per_tile, n_splits, dec_splits, dec_slots = step_tiles(ctx, plan)
+    if plan.distance_bias:
+        scratch_ptr = 0
+        if n_splits > 1:
+            floats = plan.lib.llm_attention_scratch_floats(n_tiles, plan.kv_heads, n_splits, rows_per_tile)
+            scratch_ptr = plan.scratch(ctx, int(floats), q.device).data_ptr()
+        _check(plan.lib.llm_attention_mma_bias(
+            q.data_ptr(), out.data_ptr(), out.stride(0), float(out_scale), bias.data_ptr(), bias.shape[1], cache.k_ptr,
+            cache.v_ptr, cache.block_table.data_ptr(), cache.page_stride, cache.table_stride, cache.page_tokens,
+            cache.kv_heads, cache.head_dim, ctx.seq_q_start.data_ptr(), ctx.seq_q_len.data_ptr(),
+            ctx.seq_kv_len.data_ptr(), tile_seq.data_ptr(), tile_index.data_ptr(), n_tiles, rows_per_tile, n_splits,
+            scratch_ptr, plan.heads, scale, window, ctx.stream), "attention_mma (distance bias)")
+        return
     if dec_splits and plan.decode_usable(cache):
         from . import gemm
         pool_map, box_rows = plan.decode_map(cache)

@@ -1,4 +1,4 @@
-"""Named Llama shapes for the random-weights mode of the command line tools and the benchmark.
+"""Named shapes for the random-weights mode of the command line tools and the benchmark.
 The numbers are what the respective config.json files hold; they are data for `LlamaConfig`,
 not constants of the engine."""
 
@@ -21,12 +21,45 @@ PRESETS = {
 }
 
 
+
+def _dopudra(width, vocab, positions, streams, blocks, heads, dim, ff, softmax_heads, softmax_kv, softmax_dim):
+    """`blocks` times: three lightning layers (the last with a feed-forward), then one parallel layer."""
+    decay = [1.0 - 2.0 ** -(1 + 7 * h / max(heads - 1, 1)) for h in range(heads)]
+    light = {"type": "lightning", "mixer": {"heads": heads, "dim": dim, "vdim": dim, "decay": decay}, "mlp": None}
+    both = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff},
+            "mixer": {"left": {"heads": softmax_heads, "kv_heads": softmax_kv, "dim": softmax_dim, "vdim": softmax_dim,
+                               "conv": 4, "scale": softmax_dim ** -0.5, "bias_max": positions // 2, "bias_rows": 32,
+                               "q_temp": {"coef": 0.1, "every": 128}},
+                      "right": {"heads": heads, "dim": dim, "vdim": dim, "tau": 16.0, "rank": 32},
+                      "left_scale": 1.0, "right_scale": 1.0}}
+    layers = []
+    for _ in range(blocks):
+        layers += [light, light, dict(light, mlp={"kind": "dense", "ff": ff}), both]
+    return dict(architecture="Dopudra", vocab=vocab, width=width, max_positions=positions, streams=streams,
+                embedding={"scale": 1.0}, norm={"eps": 1e-6}, layers=layers)
+
+
+PRESETS.update({
+    "dopudra-tiny": _dopudra(64, 300, 256, 2, 1, 2, 16, 96, 2, 1, 32),
+    # layer sizes near TinyLlama's (width 2048, feed-forward 5632, 32 heads of 64): 20 layers
+    "dopudra-2048": _dopudra(2048, 32000, 4096, 4, 5, 32, 64, 5632, 32, 4, 64),
+    # ... and near Llama-2-7B's (width 4096, 32 heads of 128): 32 layers
+    "dopudra-4096": _dopudra(4096, 32000, 4096, 4, 8, 32, 128, 11008, 32, 32, 128),
+})
+
+
 def preset_config(name: str, **overrides):
     from ..config.llama import LlamaConfig
     from ..errors import ConfigError
 
     if name not in PRESETS:
         raise ConfigError(f"unknown preset '{name}' (known: {sorted(PRESETS)})")
+    if "architecture" in PRESETS[name]:
+        import copy
+        from ..config.registry import resolve_architecture
+        d = copy.deepcopy(PRESETS[name])
+        d.update(overrides)
+        return resolve_architecture(d).config_class.from_dict(d)
     d = dict(PRESETS[name], architectures=["LlamaForCausalLM"])
     d.update(overrides)
     return LlamaConfig.from_dict(d)

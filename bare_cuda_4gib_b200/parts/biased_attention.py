@@ -85,6 +85,17 @@ class BiasedAttention(BranchMixer):
         rel = f(t["rel"])
         rows = distance_rows(int(self.params["max_positions"]), rel.shape[0], float(self.params["bias_far"]))
         self.bias = rel[torch.tensor(rows, device=rel.device)].t().contiguous()      # [heads, distances]
+        # bfloat16 steps with key and value heads of one size the tensor-core kernel is built for run
+        # there; everything else (float32, other sizes) runs the plain kernel
+        self.fast = None
+        if dtype == torch.bfloat16 and device.type == "cuda" and self.dim == self.vdim:
+            from ..kernels import attention as fast
+            self.fast = fast.plan_for(self.dim, self.heads, self.kv_heads, distance_bias=True)
+
+    def plan_step(self, ctx) -> None:
+        if self.fast is not None and ctx.use_fast_attention:
+            from ..kernels import attention as fast
+            fast.step_tiles(ctx, self.fast)
 
     def inner(self, ctx, cache, state, writes, u, out, out_scale) -> None:
         n, p = ctx.n_tokens, self.params
@@ -93,5 +104,10 @@ class BiasedAttention(BranchMixer):
                            float(p["eps"]), float(p["temp_coef"]), int(p["temp_every"]), writes)
         if writes:
             BA.conv_ring_write(ctx, u, state, self.taps, self.qd + self.kd + self.vd)
-        BA.attention(ctx, q, out, cache, self.bias, self.heads, float(p["scale"]),
-                     int(self.window) if self.window else 0, out_scale)
+        window = int(self.window) if self.window else 0
+        if self.fast is not None and ctx.use_fast_attention:
+            from ..kernels import attention as fast
+            if fast.usable_with_bias(out, cache):
+                fast.run(ctx, self.fast, q, out, cache, float(p["scale"]), window, self.bias, out_scale)
+                return
+        BA.attention(ctx, q, out, cache, self.bias, self.heads, float(p["scale"]), window, out_scale)

@@ -18,13 +18,14 @@ type differs from its kept type is converted on the device.
 from __future__ import annotations
 
 import fnmatch
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import TYPE_CHECKING, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
 from ..errors import WeightError
-from ..parts.spec import WeightSpec
+if TYPE_CHECKING:      # only named in signatures; importing the parts here would close an import cycle
+    from ..parts.spec import WeightSpec
 from .checkpoint import WEIGHT_FILE, Checkpoint  # noqa: F401  (WEIGHT_FILE is part of this module's surface)
 
 ARENA_ALIGN = 1024

@@ -12,11 +12,12 @@ from __future__ import annotations
 import hashlib
 import json
 import pathlib
-from typing import Dict
+from typing import TYPE_CHECKING, Dict
 
 import torch
 
-from ..parts.spec import WeightSpec
+if TYPE_CHECKING:      # only named in signatures; importing the parts here would close an import cycle
+    from ..parts.spec import WeightSpec
 from .checkpoint import WEIGHT_FILE
 from .safetensors_io import write_safetensors
 

@@ -185,6 +185,92 @@ def reference_main(args) -> int:
 SETTLE_SECONDS = 0.1      # pause between putting the prompts into the cache and the decode steps (see Bench.settle)
 
 
+def design_main(args) -> int:
+    """`--design dopudra`: one JSON line with, per size, a prefill step of `--prefill-tokens` tokens and decode
+    steps at `--batch` requests of `--context` positions for the design and for the Llama decoder of the same
+    width, both with `--design-layers` layers, seeded random weights, bfloat16, CUDA events around the steps."""
+    import torch
+
+    from bare_cuda_4gib_b200.engine.engine import LLMEngine
+    from bare_cuda_4gib_b200.engine.step import StepEntry
+    from bare_cuda_4gib_b200.kernels import gemm, lib as K
+    from bare_cuda_4gib_b200.models.presets import PRESETS, preset_config
+
+    rng = random.Random(0)
+    context, batch, warm, steps = args.context, args.batch, max(3, args.warmup), args.steps
+    tokens = min(args.prefill_tokens, context)
+
+    def measure(cfg):
+        engine = LLMEngine(None, max_tokens=context, max_seqs=batch, dtype="bfloat16", page_tokens=64,
+                           max_step_tokens=2048 + batch, use_cuda_graphs=not args.no_graphs, random=(cfg, 0))
+        runner, cache, vocab = engine.runner, engine.cache, engine.vocab_size
+        ids = lambda n: [rng.randrange(vocab) for _ in range(n)]
+        times = []
+        for i in range(args.repeats + 2):
+            slot = cache.acquire_slot()
+            piece = ids(tokens)
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            runner.step([StepEntry(slot, piece, [tokens - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            cache.release_slot(slot)
+            if i >= 2:
+                times.append(start.elapsed_time(end))
+        prefill_ms = statistics.median(times)
+        if args.only == "prefill":
+            return {"prefill_ms": prefill_ms, "prefill_tok_s": tokens / (prefill_ms / 1e3)}
+        cached = context - steps - warm - 1
+        slots = [cache.acquire_slot() for _ in range(batch)]
+        for slot in slots:
+            fed = 0
+            while fed < cached:
+                n = min(2048, cached - fed)
+                runner.step([StepEntry(slot, ids(n), [])])
+                fed += n
+        torch.cuda.synchronize()
+        time.sleep(SETTLE_SECONDS)
+        for _ in range(warm):
+            runner.step([StepEntry(s, ids(1), [0]) for s in slots])
+        runs = []
+        each = max(1, steps // args.repeats)
+        for _ in range(args.repeats):
+            torch.cuda.synchronize()
+            launches0 = K.LAUNCHES[0]
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(each):
+                runner.step([StepEntry(s, ids(1), [0]) for s in slots])
+            end.record()
+            torch.cuda.synchronize()
+            runs.append((start.elapsed_time(end) / each, (K.LAUNCHES[0] - launches0) // each))
+        gemm.check_errors()
+        decode_ms, launches = sorted(runs)[(len(runs) - 1) // 2]
+        weights = engine.model.weight_bytes()
+        del engine, runner, cache
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        return {"prefill_ms": prefill_ms, "prefill_tok_s": tokens / (prefill_ms / 1e3), "decode_ms_per_step": decode_ms,
+                "decode_tok_s": batch / (decode_ms / 1e3), "launches_per_decode_step": launches,
+                "weight_bytes": weights}
+
+    sizes = []
+    for name, closest in (("dopudra-2048", "tinyllama"), ("dopudra-4096", "llama2-7b")):
+        if args.preset not in ("tinyllama", name):       # --preset NAME: that size only
+            continue
+        layers = PRESETS[name]["layers"][: args.design_layers]
+        mine = measure(preset_config(name, layers=layers))
+        theirs = measure(preset_config(closest, num_hidden_layers=len(layers), vocab_size=PRESETS[name]["vocab"]))
+        sizes.append({"preset": name, "layers": len(layers), "width": PRESETS[name]["width"], **mine,
+                      "closest": {"preset": closest, **theirs}})
+    print(json.dumps({"design": args.design, "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random "
+                      "token ids", "prefill_tokens": tokens, "batch": batch, "context": context, "steps": steps,
+                      "warmup": warm, "repeats": args.repeats, "cuda_graphs": not args.no_graphs, "sizes": sizes}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -202,8 +288,14 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--only", default="", choices=["", "prefill", "decode"],
                     help="profiling aid: run just the prefill step or just the decode steps and print their time")
+    ap.add_argument("--design", default="", choices=["", "dopudra"],
+                    help="instead of the default workload: prefill and decode throughput of this design at layer sizes "
+                         "of real models, beside the Llama decoder at equal width, layer count and vocabulary")
+    ap.add_argument("--design-layers", type=int, default=8, help="layers of both models in a --design run")
     args = ap.parse_args()
     args.repeats = max(1, args.repeats)
+    if args.design:
+        return design_main(args)
 
     if args.impl == "reference":
         return reference_main(args)

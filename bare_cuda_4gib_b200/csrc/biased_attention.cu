@@ -41,7 +41,7 @@ __device__ __forceinline__ int cache_page(const PagedCacheKV& c, int seq, int po
 // Then q = y_q / rms(y_q) * wq * (1 + coef * ln(floor((p + 1) / every) + 1)), k = y_k / rms(y_k) * wk,
 // v = y_v; q goes to q_out, k and v into the cache.
 template <typename T>
-__global__ void conv_norm_cache_kernel(const T* __restrict__ u, long long u_stride, const float* __restrict__ conv_w,
+__global__ void __launch_bounds__(512) conv_norm_cache_kernel(const T* __restrict__ u, long long u_stride, const float* __restrict__ conv_w,
                                        int taps, const float* __restrict__ ring, const float* __restrict__ q_norm_w,
                                        const float* __restrict__ k_norm_w, T* __restrict__ q_out, PagedCacheKV cache,
                                        const int32_t* __restrict__ positions, const int32_t* __restrict__ row_seq,

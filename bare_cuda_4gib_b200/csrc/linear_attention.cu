@@ -5,8 +5,9 @@
 // where the decay a_t is one fixed number per head, or one number per key channel computed from
 // the token.  The state lives in the cache manager's state slots and is carried from step to
 // step; a step brings any number of new tokens per request (a prompt's portion or one decoded
-// token), which one kernel walks in order.  q, k and v are read as the projection left them
-// (float32 or bfloat16, rows may be strided); scores, decays, the state and the output are float32.
+// token), which one kernel walks in order.  q, k and v are read as they were stored (float32 or
+// bfloat16, rows may be strided; an activation on them is applied before, in place); scores,
+// decays, the state and the output are float32.
 //
 // Also here: the decay gate (sigmoid(z)^(1/tau) from a low-rank projection) and the gated group
 // norm that follows the scan.
@@ -17,19 +18,23 @@
 
 #define SCAN_WARPS 4
 #define SCAN_THREADS (SCAN_WARPS * 32)
-#define SCAN_ROWS 8        // state rows a thread keeps in registers
-#define SCAN_STAGE 32      // elements of the next chunk a thread holds while it works on this one
 
 #define DECAY_PER_HEAD 0
 #define DECAY_PER_CHANNEL 1
 
-__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+               : "memory");
+}
 
-// Grid (sequence, head, slice of value columns).  A warp's 32 lanes are KS row groups times
-// 32 / KS value columns; a thread owns the state elements (r * KS + kr, column) for r < SCAN_ROWS.
-// Tokens are staged through shared memory a chunk at a time: while the block walks one chunk,
-// every thread already holds its share of the next chunk's q, k, v (and decays) in registers.
-template <typename T, int ACT, int DECAY>
+// Grid (sequence, head, slice of value columns).  A warp's 32 lanes are `ks` row groups times
+// 32 / ks value columns; a thread owns the state elements (r * ks + kr, column) for r < ROWS, so a
+// token costs it ROWS multiply-adds for the state, ROWS for the output, and log2(ks) shuffles.
+// Tokens come through shared memory a chunk at a time, two chunks deep: while the block walks one
+// chunk, the next one's q, k, v (and decays) are on their way as 16-byte asynchronous copies, as
+// the projection left them (rows and head slices that are not 16-byte aligned are copied element
+// by element instead).  q_scale multiplies the output.
+template <typename T, int DECAY, int ROWS>
 __global__ void __launch_bounds__(SCAN_THREADS)
 linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                              long long q_stride, long long k_stride, long long v_stride,
@@ -38,168 +43,219 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
                              float* __restrict__ out,                  // [tokens][heads * dv]
                              const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_q_start,
                              const int32_t* __restrict__ seq_q_len, int heads, int dk, int dv, int ks, int chunk,
-                             float q_scale) {
+                             int aligned, float q_scale) {
   pdl_launch_dependents();
-  extern __shared__ float work[];   // [chunk][q dk | k dk | (a dk) | v cols]
+  extern __shared__ __align__(16) uint8_t scan_smem[];
   const int seq = blockIdx.x, head = blockIdx.y;
   const int cols_per_warp = 32 / ks;
   const int cols_per_block = cols_per_warp * SCAN_WARPS;
   const int col0 = blockIdx.z * cols_per_block;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int kr = lane % ks;
-  const int col = col0 + warp * cols_per_warp + lane / ks;
+  const int my_col = warp * cols_per_warp + lane / ks;
+  const int col = col0 + my_col;
   const bool live = col < dv;
   const int n_cols = min(cols_per_block, dv - col0);
-  const int per_token = (DECAY == DECAY_PER_CHANNEL ? 3 : 2) * dk + cols_per_block;
-  const int a_off = 2 * dk, v_off = (DECAY == DECAY_PER_CHANNEL ? 3 : 2) * dk;
+  const int tok = 2 * dk + cols_per_block;                 // elements of T per token in a buffer
+  const int t_bytes = (chunk * tok * (int)sizeof(T) + 15) & ~15;
+  const int buf_bytes = t_bytes + (DECAY == DECAY_PER_CHANNEL ? chunk * dk * 4 : 0);
   pdl_wait();
   const int n = seq_q_len[seq];
   if (n <= 0) return;
   const int row0 = seq_q_start[seq];
   const int slot = seq_slot[seq];
   float* S_g = state + (((long long)slot * heads + head) * dk) * dv;
-  float S[SCAN_ROWS];
+  float S[ROWS];
 #pragma unroll
-  for (int r = 0; r < SCAN_ROWS; ++r) {
+  for (int r = 0; r < ROWS; ++r) {
     const int i = r * ks + kr;
     S[r] = (live && i < dk) ? S_g[(long long)i * dv + col] : 0.0f;
   }
   const float head_decay = DECAY == DECAY_PER_HEAD ? decay[head] : 0.0f;
 
-  float stage[SCAN_STAGE];
-  // element e of a chunk: token e / per_token, field e % per_token
-  auto fetch = [&](int first, int count) {
-    const int total = count * per_token;
-#pragma unroll
-    for (int j = 0; j < SCAN_STAGE; ++j) {
-      const int e = threadIdx.x + j * SCAN_THREADS;
-      float val = 0.0f;
-      if (e < total) {
+  auto issue = [&](int first, int b) {
+    const int count = min(chunk, n - first);
+    T* raw = reinterpret_cast<T*>(scan_smem + (size_t)b * buf_bytes);
+    float* dec = reinterpret_cast<float*>(scan_smem + (size_t)b * buf_bytes + t_bytes);
+    if (aligned) {
+      constexpr int PER = 16 / (int)sizeof(T);               // elements per 16-byte copy
+      const int nq = dk / PER, nv = n_cols / PER, na = DECAY == DECAY_PER_CHANNEL ? dk / 4 : 0;
+      const int per_token = 2 * nq + nv + na;
+      for (int e = threadIdx.x; e < count * per_token; e += SCAN_THREADS) {
         const int t = e / per_token, f = e - t * per_token;
         const long long row = row0 + first + t;
-        if (f < dk) {
-          val = to_float(q[row * q_stride + head * dk + f]);
-          val = (ACT ? silu_f(val) : val) * q_scale;
-        } else if (f < 2 * dk) {
-          val = to_float(k[row * k_stride + head * dk + (f - dk)]);
-          if (ACT) val = silu_f(val);
-        } else if (DECAY == DECAY_PER_CHANNEL && f < 3 * dk) {
-          val = decay[row * ((long long)heads * dk) + head * dk + (f - 2 * dk)];
-        } else {
-          const int c = f - v_off;
-          if (c < n_cols) {
-            val = to_float(v[row * v_stride + head * dv + col0 + c]);
-            if (ACT) val = silu_f(val);
-          }
+        if (f < nq) cp_async_16(raw + t * tok + f * PER, q + row * q_stride + head * dk + f * PER);
+        else if (f < 2 * nq) cp_async_16(raw + t * tok + dk + (f - nq) * PER, k + row * k_stride + head * dk + (f - nq) * PER);
+        else if (f < 2 * nq + nv)
+          cp_async_16(raw + t * tok + 2 * dk + (f - 2 * nq) * PER, v + row * v_stride + head * dv + col0 + (f - 2 * nq) * PER);
+        else
+          cp_async_16(dec + t * dk + (f - 2 * nq - nv) * 4, decay + row * ((long long)heads * dk) + head * dk + (f - 2 * nq - nv) * 4);
+      }
+    } else {
+      const int per_token = 2 * dk + n_cols + (DECAY == DECAY_PER_CHANNEL ? dk : 0);
+      for (int t = 0; t < count; ++t) {
+        const long long row = row0 + first + t;
+        for (int f = threadIdx.x; f < per_token; f += SCAN_THREADS) {
+          if (f < dk) raw[t * tok + f] = q[row * q_stride + head * dk + f];
+          else if (f < 2 * dk) raw[t * tok + f] = k[row * k_stride + head * dk + (f - dk)];
+          else if (f < 2 * dk + n_cols) raw[t * tok + f] = v[row * v_stride + head * dv + col0 + (f - 2 * dk)];
+          else dec[t * dk + (f - 2 * dk - n_cols)] = decay[row * ((long long)heads * dk) + head * dk + (f - 2 * dk - n_cols)];
         }
       }
-      stage[j] = val;
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  fetch(0, min(chunk, n));
-  for (int first = 0; first < n; first += chunk) {
+
+  issue(0, 0);
+  int b = 0;
+  for (int first = 0; first < n; first += chunk, b ^= 1) {
     const int count = min(chunk, n - first);
-    __syncthreads();   // the chunk before this one has been walked
-#pragma unroll
-    for (int j = 0; j < SCAN_STAGE; ++j) {
-      const int e = threadIdx.x + j * SCAN_THREADS;
-      if (e < count * per_token) work[e] = stage[j];
-    }
-    __syncthreads();
-    if (first + chunk < n) fetch(first + chunk, min(chunk, n - first - chunk));
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();   // this chunk has landed, and the chunk before it has been walked by every warp
+    if (first + chunk < n) issue(first + chunk, b ^ 1);
+    const T* raw = reinterpret_cast<const T*>(scan_smem + (size_t)b * buf_bytes);
+    const float* dec = reinterpret_cast<const float*>(scan_smem + (size_t)b * buf_bytes + t_bytes);
+    float* o_row = out + (long long)(row0 + first) * ((long long)heads * dv) + head * dv + col;
+#pragma unroll 2
     for (int t = 0; t < count; ++t) {
-      const float* w = work + t * per_token;
-      const float vv = w[v_off + warp * cols_per_warp + lane / ks];
+      const T* w = raw + t * tok;
+      const float vv = to_float(w[2 * dk + my_col]);
       float acc = 0.0f;
 #pragma unroll
-      for (int r = 0; r < SCAN_ROWS; ++r) {
+      for (int r = 0; r < ROWS; ++r) {
         const int i = r * ks + kr;
         if (i < dk) {
-          const float a = DECAY == DECAY_PER_CHANNEL ? w[a_off + i] : head_decay;
-          S[r] = a * S[r] + w[dk + i] * vv;
-          acc += S[r] * w[i];
+          const float a = DECAY == DECAY_PER_CHANNEL ? dec[t * dk + i] : head_decay;
+          S[r] = a * S[r] + to_float(w[dk + i]) * vv;
+          acc += S[r] * to_float(w[i]);
         }
       }
       for (int o = ks >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (live && kr == 0) out[(long long)(row0 + first + t) * ((long long)heads * dv) + head * dv + col] = acc;
+      if (live && kr == 0) o_row[(long long)t * ((long long)heads * dv)] = acc * q_scale;
     }
   }
 #pragma unroll
-  for (int r = 0; r < SCAN_ROWS; ++r) {
+  for (int r = 0; r < ROWS; ++r) {
     const int i = r * ks + kr;
     if (live && i < dk) S_g[(long long)i * dv + col] = S[r];
   }
 }
 
+template <typename T, int DECAY, int ROWS>
+static int scan_launch(dim3 grid, size_t smem, cudaStream_t stream, const void* q, const void* k, const void* v,
+                       long long q_stride, long long k_stride, long long v_stride, const float* decay, float* state,
+                       float* out, const int32_t* seq_slot, const int32_t* seq_q_start, const int32_t* seq_q_len,
+                       int heads, int dk, int dv, int ks, int chunk, int aligned, float q_scale) {
+  auto kern = linear_attention_scan_kernel<T, DECAY, ROWS>;
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return launch_status();
+  launch_kernel(kern, grid, SCAN_THREADS, smem, stream, (const T*)q, (const T*)k, (const T*)v, q_stride, k_stride,
+                v_stride, decay, state, out, seq_slot, seq_q_start, seq_q_len, heads, dk, dv, ks, chunk, aligned, q_scale);
+  return launch_status();
+}
+
 extern "C" int llm_linear_attention_scan(const void* q, const void* k, const void* v, int dtype, long long q_stride,
                                          long long k_stride, long long v_stride, const float* decay, int per_channel,
-                                         int act_silu, float* state, float* out, const int32_t* seq_slot,
+                                         float* state, float* out, const int32_t* seq_slot,
                                          const int32_t* seq_q_start, const int32_t* seq_q_len, int n_seqs, int heads,
                                          int dk, int dv, float q_scale, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
-  LLM_HOST_CHECK(dk >= 1 && dk <= 32 * SCAN_ROWS && dv >= 1 && heads >= 1, ERR_BAD_SIZE);
+  LLM_HOST_CHECK(dk >= 1 && dk <= 256 && dv >= 1 && heads >= 1 && heads <= 65535, ERR_BAD_SIZE);
+  LLM_HOST_CHECK(dtype == DT_F32 || dtype == DT_BF16, ERR_BAD_DTYPE);
+  const int rows = dk <= 128 ? 4 : 8;
   int ks = 1;
-  while (ks * SCAN_ROWS < dk) ks <<= 1;          // row groups: a power of two, at most 32
+  while (ks * rows < dk) ks <<= 1;          // row groups: a power of two, at most 32
   const int cols_per_block = (32 / ks) * SCAN_WARPS;
   const int slices = (dv + cols_per_block - 1) / cols_per_block;
-  const int per_token = (per_channel ? 3 : 2) * dk + cols_per_block;
-  int chunk = SCAN_STAGE * SCAN_THREADS / per_token;
-  if (chunk > 16) chunk = 16;
-  LLM_HOST_CHECK(chunk >= 1, ERR_BAD_SIZE);
-  const size_t smem = (size_t)chunk * per_token * sizeof(float);
+  const int esize = dtype == DT_F32 ? 4 : 2;
+  const int token_bytes = (2 * dk + cols_per_block) * esize + (per_channel ? dk * 4 : 0);
+  int chunk = 16;
+  while (chunk > 2 && chunk * token_bytes > 24 * 1024) chunk >>= 1;
+  const size_t smem = 2 * (size_t)(((chunk * (2 * dk + cols_per_block) * esize + 15) & ~15) + (per_channel ? chunk * dk * 4 : 0));
+  LLM_HOST_CHECK(smem <= 200 * 1024, ERR_BAD_SIZE);
+  // 16-byte copies need every head slice of every row to start and end on a 16-byte boundary
+  const int per = 16 / esize;
+  auto ok = [&](const void* p, long long stride) { return ((uintptr_t)p % 16) == 0 && stride % per == 0; };
+  int aligned = ok(q, q_stride) && ok(k, k_stride) && ok(v, v_stride) && dk % per == 0 && dv % per == 0 &&
+                cols_per_block % per == 0 && (!per_channel || (dk % 4 == 0 && ((uintptr_t)decay % 16) == 0));
   dim3 grid(n_seqs, heads, slices);
-#define LAUNCH(T, ACT, DEC)                                                                                     \
-  launch_kernel(linear_attention_scan_kernel<T, ACT, DEC>, grid, SCAN_THREADS, smem, stream, (const T*)q,       \
-                (const T*)k, (const T*)v, q_stride, k_stride, v_stride, decay, state, out, seq_slot, seq_q_start, \
-                seq_q_len, heads, dk, dv, ks, chunk, q_scale)
+#define GO(T, DEC, ROWS)                                                                                         \
+  return scan_launch<T, DEC, ROWS>(grid, smem, stream, q, k, v, q_stride, k_stride, v_stride, decay, state, out, \
+                                   seq_slot, seq_q_start, seq_q_len, heads, dk, dv, ks, chunk, aligned, q_scale)
   if (dtype == DT_F32) {
-    if (per_channel) { if (act_silu) LAUNCH(float, 1, 1); else LAUNCH(float, 0, 1); }
-    else { if (act_silu) LAUNCH(float, 1, 0); else LAUNCH(float, 0, 0); }
-  } else if (dtype == DT_BF16) {
-    if (per_channel) { if (act_silu) LAUNCH(__nv_bfloat16, 1, 1); else LAUNCH(__nv_bfloat16, 0, 1); }
-    else { if (act_silu) LAUNCH(__nv_bfloat16, 1, 0); else LAUNCH(__nv_bfloat16, 0, 0); }
+    if (per_channel) { if (rows == 4) GO(float, 1, 4); else GO(float, 1, 8); }
+    else { if (rows == 4) GO(float, 0, 4); else GO(float, 0, 8); }
   } else {
-    return ERR_BAD_DTYPE;
+    if (per_channel) { if (rows == 4) GO(__nv_bfloat16, 1, 4); else GO(__nv_bfloat16, 1, 8); }
+    else { if (rows == 4) GO(__nv_bfloat16, 0, 4); else GO(__nv_bfloat16, 0, 8); }
   }
-#undef LAUNCH
-  return launch_status();
+#undef GO
 }
 
 // ----------------------------------------------------------------------------- decay gate
 
+#define GATE_ROWS 16      // token rows a block takes
+#define GATE_THREADS 128  // channels a block takes
+
 // a[t][c] = sigmoid(z)^(1/tau), z = sum_r up[c][r] low[t][r] + bias[c], as exp(-softplus(-z) / tau).
+// A block takes GATE_ROWS tokens and GATE_THREADS channels; a thread owns one channel, reads its
+// row of `up` once, eight numbers at a time, and uses it for every token of the block.
 template <typename T>
-__global__ void decay_gate_kernel(const T* __restrict__ low, long long low_stride, const float* __restrict__ up,
-                                  const float* __restrict__ bias, float* __restrict__ out, int channels, int rank,
-                                  float inv_tau) {
+__global__ void __launch_bounds__(GATE_THREADS)
+decay_gate_kernel(const T* __restrict__ low, long long low_stride, const float* __restrict__ up,
+                  const float* __restrict__ bias, float* __restrict__ out, int rows, int channels, int rank,
+                  float inv_tau) {
   pdl_launch_dependents();
-  extern __shared__ float low_row[];
+  extern __shared__ float low_rows[];    // [GATE_ROWS][rank]
   pdl_wait();
-  const long long t = blockIdx.x;
-  for (int r = threadIdx.x; r < rank; r += blockDim.x) low_row[r] = to_float(low[t * low_stride + r]);
+  const int t0 = blockIdx.y * GATE_ROWS;
+  const int n = min(GATE_ROWS, rows - t0);
+  for (int e = threadIdx.x; e < n * rank; e += GATE_THREADS)
+    low_rows[e] = to_float(low[(long long)(t0 + e / rank) * low_stride + e % rank]);
   __syncthreads();
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-    float z = 0.0f;
-    const float* urow = up + (long long)c * rank;
-    for (int r = 0; r < rank; ++r) z += urow[r] * low_row[r];
-    if (bias) z += bias[c];
-    const float sp = fmaxf(-z, 0.0f) + log1pf(expf(-fabsf(z)));   // softplus(-z)
-    out[t * channels + c] = expf(-sp * inv_tau);
+  const int c = blockIdx.x * GATE_THREADS + threadIdx.x;
+  if (c >= channels) return;
+  float z[GATE_ROWS];
+#pragma unroll
+  for (int t = 0; t < GATE_ROWS; ++t) z[t] = 0.0f;
+  const float* urow = up + (long long)c * rank;
+  for (int r0 = 0; r0 < rank; r0 += 8) {
+    float w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) w[j] = r0 + j < rank ? urow[r0 + j] : 0.0f;
+#pragma unroll
+    for (int t = 0; t < GATE_ROWS; ++t) {
+      if (t < n) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (r0 + j < rank) z[t] += w[j] * low_rows[t * rank + r0 + j];
+      }
+    }
+  }
+  const float b = bias ? bias[c] : 0.0f;
+#pragma unroll
+  for (int t = 0; t < GATE_ROWS; ++t) {
+    if (t < n) {
+      const float zz = z[t] + b;
+      const float sp = fmaxf(-zz, 0.0f) + log1pf(expf(-fabsf(zz)));   // softplus(-z)
+      out[(long long)(t0 + t) * channels + c] = expf(-sp * inv_tau);
+    }
   }
 }
 
 extern "C" int llm_decay_gate(const void* low, int dtype, long long low_stride, const float* up, const float* bias,
                               float* out, int rows, int channels, int rank, float inv_tau, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  const size_t smem = (size_t)rank * sizeof(float);
+  const size_t smem = (size_t)GATE_ROWS * rank * sizeof(float);
   LLM_HOST_CHECK(smem <= 48 * 1024, ERR_BAD_SIZE);
-  const int threads = channels >= 1024 ? 256 : 128;
+  dim3 grid((channels + GATE_THREADS - 1) / GATE_THREADS, (rows + GATE_ROWS - 1) / GATE_ROWS);
+  LLM_HOST_CHECK(grid.y <= 65535, ERR_BAD_SIZE);
   if (dtype == DT_F32)
-    launch_kernel(decay_gate_kernel<float>, rows, threads, smem, stream, (const float*)low, low_stride, up, bias, out,
-                  channels, rank, inv_tau);
+    launch_kernel(decay_gate_kernel<float>, grid, GATE_THREADS, smem, stream, (const float*)low, low_stride, up, bias,
+                  out, rows, channels, rank, inv_tau);
   else if (dtype == DT_BF16)
-    launch_kernel(decay_gate_kernel<__nv_bfloat16>, rows, threads, smem, stream, (const __nv_bfloat16*)low, low_stride,
-                  up, bias, out, channels, rank, inv_tau);
+    launch_kernel(decay_gate_kernel<__nv_bfloat16>, grid, GATE_THREADS, smem, stream, (const __nv_bfloat16*)low,
+                  low_stride, up, bias, out, rows, channels, rank, inv_tau);
   else
     return ERR_BAD_DTYPE;
   return launch_status();
@@ -210,27 +266,30 @@ extern "C" int llm_decay_gate(const void* low, int dtype, long long low_stride, 
 #define GATE_SIGMOID 0
 #define GATE_SILU 1
 
-// One warp per (row, group): out = x / sqrt(mean_group(x^2) + eps) * weight[c % weight_len] *
-// gate_act(gate) * out_scale.  A group is `group` neighbouring channels of the row.
-template <typename TG, typename TO>
+// One warp (WIDE: one block of 256 threads) per (row, group): out = x / sqrt(mean_group(x^2) + eps) *
+// weight[c % weight_len] * gate_act(gate) * out_scale.  A group is `group` neighbouring channels
+// of the row.  Which form runs depends on the group's size only.
+template <typename TG, typename TO, bool WIDE>
 __global__ void gated_group_norm_kernel(const float* __restrict__ x, const TG* __restrict__ gate, long long gate_stride,
                                         const float* __restrict__ weight, int weight_len, TO* __restrict__ out,
                                         long long out_stride, int rows, int channels, int group, int gate_kind,
                                         float eps, float out_scale) {
   pdl_launch_dependents();
   pdl_wait();
+  __shared__ float scratch[32];
   const int groups = channels / group;
-  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long item = WIDE ? (long long)blockIdx.x : (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= (long long)rows * groups) return;
   const long long r = item / groups;
   const int g = (int)(item - r * groups);
-  const int lane = threadIdx.x & 31;
+  const int lane = WIDE ? threadIdx.x : threadIdx.x & 31;
+  const int step = WIDE ? blockDim.x : 32;
   const float* xr = x + r * channels + (long long)g * group;
   float sq = 0.0f;
-  for (int i = lane; i < group; i += 32) sq += xr[i] * xr[i];
-  sq = warp_sum(sq);
+  for (int i = lane; i < group; i += step) sq += xr[i] * xr[i];
+  sq = WIDE ? block_sum(sq, scratch) : warp_sum(sq);
   const float scale = 1.0f / sqrtf(sq / (float)group + eps);
-  for (int i = lane; i < group; i += 32) {
+  for (int i = lane; i < group; i += step) {
     const int c = g * group + i;
     const float z = to_float(gate[r * gate_stride + c]);
     const float gz = gate_kind == GATE_SILU ? z / (1.0f + expf(-z)) : 1.0f / (1.0f + expf(-z));
@@ -246,10 +305,18 @@ extern "C" int llm_gated_group_norm(const float* x, const void* gate, int gate_d
   LLM_HOST_CHECK(group >= 1 && channels % group == 0 && weight_len >= 1, ERR_BAD_SIZE);
   const long long items = (long long)rows * (channels / group);
   const int warps = 4;
-  const int blocks = (int)((items + warps - 1) / warps);
-#define LAUNCH(TG, TO)                                                                                      \
-  launch_kernel(gated_group_norm_kernel<TG, TO>, blocks, warps * 32, 0, stream, x, (const TG*)gate, gate_stride, \
-                weight, weight_len, (TO*)out, out_stride, rows, channels, group, gate_kind, eps, out_scale)
+  const bool wide = group >= 512;
+  const int blocks = wide ? (int)items : (int)((items + warps - 1) / warps);
+#define LAUNCH(TG, TO)                                                                                            \
+  do {                                                                                                            \
+    if (wide)                                                                                                     \
+      launch_kernel(gated_group_norm_kernel<TG, TO, true>, blocks, 256, 0, stream, x, (const TG*)gate, gate_stride, \
+                    weight, weight_len, (TO*)out, out_stride, rows, channels, group, gate_kind, eps, out_scale);  \
+    else                                                                                                          \
+      launch_kernel(gated_group_norm_kernel<TG, TO, false>, blocks, warps * 32, 0, stream, x, (const TG*)gate,    \
+                    gate_stride, weight, weight_len, (TO*)out, out_stride, rows, channels, group, gate_kind, eps, \
+                    out_scale);                                                                                   \
+  } while (0)
   if (gate_dtype == DT_F32 && out_dtype == DT_F32) LAUNCH(float, float);
   else if (gate_dtype == DT_BF16 && out_dtype == DT_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (gate_dtype == DT_F32 && out_dtype == DT_BF16) LAUNCH(float, __nv_bfloat16);

@@ -55,8 +55,9 @@ extern "C" int llm_embed_positions(const void* table, const void* pos_table, int
 //   y = sum(delta partials) * delta_scale;  x_t <- sum_s mix[s][t] x_s + write[t] * y   for every t,
 // all from the old streams, written back.  Then u = sum_t read[t] x_t (read == nullptr: plain sum)
 // and out = u / sqrt(mean(u^2) + eps) * weight.
-template <typename TD, typename TO>
-__global__ void stream_step_kernel(float* __restrict__ streams_buf, int n_streams, const TD* __restrict__ delta,
+// SMAX bounds the number of streams at compile time (the loops over streams are unrolled to it).
+template <typename TD, typename TO, int SMAX>
+__global__ void __launch_bounds__(256) stream_step_kernel(float* __restrict__ streams_buf, int n_streams, const TD* __restrict__ delta,
                                    int n_partials, long long partial_stride, long long delta_row_stride,
                                    const float* __restrict__ delta_scale, const float* __restrict__ write_vec,
                                    const float* __restrict__ mix, const float* __restrict__ read_vec,
@@ -82,9 +83,9 @@ __global__ void stream_step_kernel(float* __restrict__ streams_buf, int n_stream
   float* x = streams_buf + src * S * width;
   float sq = 0.0f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float xs[MAX_STREAMS];
+    float xs[SMAX];
 #pragma unroll
-    for (int s = 0; s < MAX_STREAMS; ++s)
+    for (int s = 0; s < SMAX; ++s)
       if (s < S) xs[s] = x[(long long)s * width + i];
     float u = 0.0f;
     if (delta) {
@@ -92,11 +93,11 @@ __global__ void stream_step_kernel(float* __restrict__ streams_buf, int n_stream
       for (int p = 0; p < n_partials; ++p) y += to_float(delta[p * partial_stride + src * delta_row_stride + i]);
       if (delta_scale) y *= delta_scale[i];
 #pragma unroll
-      for (int t = 0; t < MAX_STREAMS; ++t) {
+      for (int t = 0; t < SMAX; ++t) {
         if (t < S) {
           float v = 0.0f;
 #pragma unroll
-          for (int s = 0; s < MAX_STREAMS; ++s)
+          for (int s = 0; s < SMAX; ++s)
             if (s < S) v += s_mix[s * S + t] * xs[s];
           v += s_write[t] * y;
           x[(long long)t * width + i] = v;
@@ -105,7 +106,7 @@ __global__ void stream_step_kernel(float* __restrict__ streams_buf, int n_stream
       }
     } else {
 #pragma unroll
-      for (int t = 0; t < MAX_STREAMS; ++t)
+      for (int t = 0; t < SMAX; ++t)
         if (t < S) u += s_read[t] * xs[t];
     }
     u_row[i] = u;
@@ -125,16 +126,25 @@ extern "C" int llm_stream_step(float* streams_buf, int n_streams, const void* de
                                cudaStream_t stream) {
   if (rows <= 0) return 0;
   LLM_HOST_CHECK(n_streams >= 1 && n_streams <= MAX_STREAMS, ERR_BAD_SIZE);
-  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  const int threads = width >= 512 ? 256 : 128;   // (__launch_bounds__ of the kernel)
   const size_t smem = (size_t)(width + 32 + MAX_STREAMS * MAX_STREAMS + 2 * MAX_STREAMS) * sizeof(float);
   LLM_HOST_CHECK(smem <= 200 * 1024, ERR_BAD_SIZE);
-#define LAUNCH(TD, TO)                                                                                         \
+#define LAUNCH_S(TD, TO, SMAX)                                                                                 \
   do {                                                                                                         \
     if (smem > 48 * 1024)                                                                                      \
-      cudaFuncSetAttribute(stream_step_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    launch_kernel(stream_step_kernel<TD, TO>, rows, threads, smem, stream, streams_buf, n_streams,             \
+      cudaFuncSetAttribute(stream_step_kernel<TD, TO, SMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                           (int)smem);                                                                         \
+    launch_kernel(stream_step_kernel<TD, TO, SMAX>, rows, threads, smem, stream, streams_buf, n_streams,       \
                   (const TD*)delta, n_partials, partial_stride, delta_row_stride, delta_scale, write_vec, mix,  \
                   read_vec, weight, (TO*)out, row_index, width, eps);                                          \
+  } while (0)
+#define LAUNCH(TD, TO)                                     \
+  do {                                                     \
+    if (n_streams == 1) LAUNCH_S(TD, TO, 1);               \
+    else if (n_streams <= 2) LAUNCH_S(TD, TO, 2);          \
+    else if (n_streams <= 4) LAUNCH_S(TD, TO, 4);          \
+    else if (n_streams <= 8) LAUNCH_S(TD, TO, 8);          \
+    else LAUNCH_S(TD, TO, MAX_STREAMS);                    \
   } while (0)
   if (delta_dtype == DT_F32 && out_dtype == DT_F32) LAUNCH(float, float);
   else if (delta_dtype == DT_F32 && out_dtype == DT_BF16) LAUNCH(float, __nv_bfloat16);
@@ -142,6 +152,7 @@ extern "C" int llm_stream_step(float* streams_buf, int n_streams, const void* de
   else if (delta_dtype == DT_BF16 && out_dtype == DT_F32) LAUNCH(__nv_bfloat16, float);
   else return ERR_BAD_DTYPE;
 #undef LAUNCH
+#undef LAUNCH_S
   return launch_status();
 }
 
@@ -161,10 +172,11 @@ __device__ __forceinline__ float activate(float z, int kind) {
   }
 }
 
-// out[r][c] = act(sum of partials in[p][r][c]); rows of `in` and `out` may be strided.
+// out[r][c] = act(sum of partials in[p][r][c]); rows of `in` and `out` may be strided, and `out`
+// may be `in` itself (one partial, equal types and strides).
 template <typename TI, typename TO>
-__global__ void activation_kernel(const TI* __restrict__ in, int n_partials, long long partial_stride,
-                                  long long in_stride, TO* __restrict__ out, long long out_stride, int rows,
+__global__ void activation_kernel(const TI* in, int n_partials, long long partial_stride,
+                                  long long in_stride, TO* out, long long out_stride, int rows,
                                   int width, int kind) {
   pdl_launch_dependents();
   pdl_wait();

@@ -23,7 +23,7 @@ def lib():
     if _lib is None:
         l = build.load_library("linear_attention.cu")
         P, I, L, F = c_void_p, c_int, c_longlong, c_float
-        l.llm_linear_attention_scan.argtypes = [P, P, P, I, L, L, L, P, I, I, P, P, P, P, P, I, I, I, I, F, P]
+        l.llm_linear_attention_scan.argtypes = [P, P, P, I, L, L, L, P, I, P, P, P, P, P, I, I, I, I, F, P]
         l.llm_decay_gate.argtypes = [P, I, L, P, P, P, I, I, I, F, P]
         l.llm_gated_group_norm.argtypes = [P, P, I, L, P, I, P, I, L, I, I, I, I, F, F, P]
         for name in ("llm_linear_attention_scan", "llm_decay_gate", "llm_gated_group_norm"):
@@ -33,19 +33,19 @@ def lib():
 
 
 def scan(ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, per_channel: bool,
-         silu: bool, state: torch.Tensor, out: torch.Tensor, heads: int, dk: int, dv: int, q_scale: float = 1.0) -> None:
+         state: torch.Tensor, out: torch.Tensor, heads: int, dk: int, dv: int, q_scale: float = 1.0) -> None:
     """For every sequence of the step, in token order: S = diag(a) S + k v^T, o = S^T (q * q_scale),
     with S in `state[slot]` ([heads, dk, dv] float32) read at the start and written at the end.
     q, k [rows, heads * dk] and v [rows, heads * dv] may be column views of a wider matrix;
-    `decay` is [heads] or, with `per_channel`, [rows, heads * dk] float32; `silu` applies
-    z * sigmoid(z) to q, k and v as they are read.  out [rows, heads * dv] float32."""
+    `decay` is [heads] or, with `per_channel`, [rows, heads * dk] float32.  out [rows, heads * dv]
+    float32."""
     _dev(q, k, v, decay, state, out)
     if not (q.dtype == k.dtype == v.dtype) or state.dtype != torch.float32 or out.dtype != torch.float32 \
             or decay.dtype != torch.float32 or not out.is_contiguous() or not decay.is_contiguous():
         raise KernelLaunchError("linear_attention_scan: element types or layout not as the kernel needs")
     _check(lib().llm_linear_attention_scan(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), dtype_code(q.dtype), q.stride(0), k.stride(0), v.stride(0),
-        decay.data_ptr(), 1 if per_channel else 0, 1 if silu else 0, state.data_ptr(), out.data_ptr(),
+        decay.data_ptr(), 1 if per_channel else 0, state.data_ptr(), out.data_ptr(),
         ctx.seq_slot.data_ptr(), ctx.seq_q_start.data_ptr(), ctx.seq_q_len.data_ptr(), ctx.n_seqs, heads, dk, dv,
         float(q_scale), ctx.stream), "linear_attention_scan")
 

@@ -24,7 +24,7 @@ from __future__ import annotations
 import torch
 
 from ..errors import ConfigError
-from ..kernels import linear_attention as LA
+from ..kernels import lib as K, linear_attention as LA, streams as SK
 from .base import Part, StateRequest
 from .linear import Linear
 from .registry import register_mixer
@@ -110,8 +110,11 @@ class LightningAttention(_LinearAttention):
     def inner(self, ctx, cache, state, writes, u, out, out_scale) -> None:
         n = ctx.n_tokens
         q, k, v, g = self._split(u)
+        # silu on q, k and v where the projection left them (they are neighbouring columns)
+        qkv = u[:, : 2 * self.heads * self.dim + self.heads * self.vdim]
+        SK.activation(K.Partials(qkv), qkv, n, "silu", ctx.stream)
         o = ctx.ws.get("scan_out", (n, self.heads * self.vdim), torch.float32)
-        LA.scan(ctx, q, k, v, self.decay, False, True, state, o, self.heads, self.dim, self.vdim)
+        LA.scan(ctx, q, k, v, self.decay, False, state, o, self.heads, self.dim, self.vdim)
         LA.gated_group_norm(o, g, self.norm_w, out, n, self.heads * self.vdim, "sigmoid", self.eps, out_scale, ctx.stream)
 
 
@@ -142,5 +145,5 @@ class GatedLinearAttention(_LinearAttention):
         a = ctx.ws.get("scan_decay", (n, self.heads * self.dim), torch.float32)
         LA.decay_gate(low, self.a2, self.a2_bias, a, n, self.tau, ctx.stream)
         o = ctx.ws.get("scan_out", (n, self.heads * self.vdim), torch.float32)
-        LA.scan(ctx, q, k, v, a, True, False, state, o, self.heads, self.dim, self.vdim, self.dim ** -0.5)
+        LA.scan(ctx, q, k, v, a, True, state, o, self.heads, self.dim, self.vdim, self.dim ** -0.5)
         LA.gated_group_norm(o, g, self.norm_w, out, n, self.vdim, "silu", self.eps, out_scale, ctx.stream)

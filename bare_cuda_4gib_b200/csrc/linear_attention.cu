@@ -16,8 +16,9 @@
 
 #include <math.h>
 
-#define SCAN_WARPS 4
+#define SCAN_WARPS 2
 #define SCAN_THREADS (SCAN_WARPS * 32)
+#define SCAN_BUFFERS 4     // chunks in shared memory: one being walked, the others on their way
 
 #define DECAY_PER_HEAD 0
 #define DECAY_PER_CHANNEL 1
@@ -27,14 +28,42 @@ __device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
                : "memory");
 }
 
+// ROWS numbers starting at p (16-byte aligned when VEC) as floats.
+template <typename T, int ROWS, bool VEC>
+__device__ __forceinline__ void load_rows(const T* p, int valid, float (&dst)[ROWS]) {
+  if constexpr (VEC && sizeof(T) == 2) {
+#pragma unroll
+    for (int j = 0; j < ROWS / 8; ++j) {
+      const uint4 raw = reinterpret_cast<const uint4*>(p)[j];
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        dst[j * 8 + 2 * e] = __uint_as_float(w[e] << 16);
+        dst[j * 8 + 2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+      }
+    }
+  } else if constexpr (VEC) {
+#pragma unroll
+    for (int j = 0; j < ROWS / 4; ++j) {
+      const float4 raw = reinterpret_cast<const float4*>(p)[j];
+      dst[j * 4] = raw.x; dst[j * 4 + 1] = raw.y; dst[j * 4 + 2] = raw.z; dst[j * 4 + 3] = raw.w;
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) dst[r] = r < valid ? to_float(p[r]) : 0.0f;
+  }
+}
+
 // Grid (sequence, head, slice of value columns).  A warp's 32 lanes are `ks` row groups times
-// 32 / ks value columns; a thread owns the state elements (r * ks + kr, column) for r < ROWS, so a
-// token costs it ROWS multiply-adds for the state, ROWS for the output, and log2(ks) shuffles.
-// Tokens come through shared memory a chunk at a time, two chunks deep: while the block walks one
-// chunk, the next one's q, k, v (and decays) are on their way as 16-byte asynchronous copies, as
+// 32 / ks value columns; a thread owns the ROWS neighbouring state rows kr * ROWS .. of one column,
+// so a token costs it ROWS multiply-adds for the state, ROWS for the output, log2(ks) shuffles, and
+// (VEC: rows and buffers 16-byte aligned, every thread's rows inside the key size) a few 16-byte
+// loads of q and k from shared memory.
+// Tokens come through shared memory a chunk at a time, SCAN_BUFFERS chunks deep: while the block walks
+// one chunk, the next ones' q, k, v (and decays) are on their way as 16-byte asynchronous copies, as
 // the projection left them (rows and head slices that are not 16-byte aligned are copied element
 // by element instead).  q_scale multiplies the output.
-template <typename T, int DECAY, int ROWS>
+template <typename T, int DECAY, int ROWS, bool VEC>
 __global__ void __launch_bounds__(SCAN_THREADS)
 linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                              long long q_stride, long long k_stride, long long v_stride,
@@ -68,9 +97,10 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
   float S[ROWS];
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
-    const int i = r * ks + kr;
+    const int i = kr * ROWS + r;
     S[r] = (live && i < dk) ? S_g[(long long)i * dv + col] : 0.0f;
   }
+  const int valid = min(ROWS, dk - kr * ROWS);     // rows of this thread inside the key size (may be <= 0)
   const float head_decay = DECAY == DECAY_PER_HEAD ? decay[head] : 0.0f;
 
   auto issue = [&](int first, int b) {
@@ -106,47 +136,76 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  issue(0, 0);
+  // one group of copies per chunk, empty past the end, so that "all but the newest SCAN_BUFFERS - 2
+  // groups have landed" always means "this chunk has landed"
+#pragma unroll
+  for (int j = 0; j < SCAN_BUFFERS - 1; ++j) {
+    if (j * chunk < n) issue(j * chunk, j);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   int b = 0;
-  for (int first = 0; first < n; first += chunk, b ^= 1) {
+  for (int first = 0; first < n; first += chunk, b = (b + 1) % SCAN_BUFFERS) {
     const int count = min(chunk, n - first);
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("cp.async.wait_group %0;" ::"n"(SCAN_BUFFERS - 2) : "memory");
     __syncthreads();   // this chunk has landed, and the chunk before it has been walked by every warp
-    if (first + chunk < n) issue(first + chunk, b ^ 1);
+    if (first + (SCAN_BUFFERS - 1) * chunk < n) issue(first + (SCAN_BUFFERS - 1) * chunk, (b + SCAN_BUFFERS - 1) % SCAN_BUFFERS);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
     const T* raw = reinterpret_cast<const T*>(scan_smem + (size_t)b * buf_bytes);
     const float* dec = reinterpret_cast<const float*>(scan_smem + (size_t)b * buf_bytes + t_bytes);
     float* o_row = out + (long long)(row0 + first) * ((long long)heads * dv) + head * dv + col;
-#pragma unroll 2
-    for (int t = 0; t < count; ++t) {
+    // tokens in groups: a group's loads and products are independent of one another but for the one
+    // multiply-add per state element that carries the state on, and its reductions run side by side
+    constexpr int GROUP = DECAY == DECAY_PER_CHANNEL ? 2 : 4;
+    const int at = valid > 0 ? kr * ROWS : 0;
+    auto token = [&](int t) -> float {
       const T* w = raw + t * tok;
       const float vv = to_float(w[2 * dk + my_col]);
-      float acc = 0.0f;
+      float qq[ROWS], kk[ROWS], aa[ROWS];
+      load_rows<T, ROWS, VEC>(w + at, valid, qq);
+      load_rows<T, ROWS, VEC>(w + dk + at, valid, kk);
+      if (DECAY == DECAY_PER_CHANNEL) load_rows<float, ROWS, VEC>(dec + t * dk + at, valid, aa);
+      float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) {
-        const int i = r * ks + kr;
-        if (i < dk) {
-          const float a = DECAY == DECAY_PER_CHANNEL ? dec[t * dk + i] : head_decay;
-          S[r] = a * S[r] + to_float(w[dk + i]) * vv;
-          acc += S[r] * to_float(w[i]);
-        }
+        const float a = DECAY == DECAY_PER_CHANNEL ? aa[r] : head_decay;
+        S[r] = a * S[r] + kk[r] * vv;
+        part[r & 3] += S[r] * qq[r];
       }
+      return (part[0] + part[1]) + (part[2] + part[3]);
+    };
+    int t0 = 0;
+    for (; t0 + GROUP <= count; t0 += GROUP) {      // whole groups: straight-line code
+      float accs[GROUP];
+#pragma unroll
+      for (int g = 0; g < GROUP; ++g) accs[g] = token(t0 + g);
+      for (int o = ks >> 1; o > 0; o >>= 1) {
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g) accs[g] += __shfl_xor_sync(0xffffffffu, accs[g], o);
+      }
+      if (live && kr == 0) {
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g) o_row[(long long)(t0 + g) * ((long long)heads * dv)] = accs[g] * q_scale;
+      }
+    }
+    for (; t0 < count; ++t0) {                       // the chunk's last tokens
+      float acc = token(t0);
       for (int o = ks >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (live && kr == 0) o_row[(long long)t * ((long long)heads * dv)] = acc * q_scale;
+      if (live && kr == 0) o_row[(long long)t0 * ((long long)heads * dv)] = acc * q_scale;
     }
   }
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
-    const int i = r * ks + kr;
+    const int i = kr * ROWS + r;
     if (live && i < dk) S_g[(long long)i * dv + col] = S[r];
   }
 }
 
-template <typename T, int DECAY, int ROWS>
+template <typename T, int DECAY, int ROWS, bool VEC>
 static int scan_launch(dim3 grid, size_t smem, cudaStream_t stream, const void* q, const void* k, const void* v,
                        long long q_stride, long long k_stride, long long v_stride, const float* decay, float* state,
                        float* out, const int32_t* seq_slot, const int32_t* seq_q_start, const int32_t* seq_q_len,
                        int heads, int dk, int dv, int ks, int chunk, int aligned, float q_scale) {
-  auto kern = linear_attention_scan_kernel<T, DECAY, ROWS>;
+  auto kern = linear_attention_scan_kernel<T, DECAY, ROWS, VEC>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return launch_status();
   launch_kernel(kern, grid, SCAN_THREADS, smem, stream, (const T*)q, (const T*)k, (const T*)v, q_stride, k_stride,
@@ -162,16 +221,16 @@ extern "C" int llm_linear_attention_scan(const void* q, const void* k, const voi
   if (n_seqs <= 0) return 0;
   LLM_HOST_CHECK(dk >= 1 && dk <= 256 && dv >= 1 && heads >= 1 && heads <= 65535, ERR_BAD_SIZE);
   LLM_HOST_CHECK(dtype == DT_F32 || dtype == DT_BF16, ERR_BAD_DTYPE);
-  const int rows = dk <= 128 ? 4 : 8;
+  const int rows = dk <= 32 ? 8 : 16;
   int ks = 1;
-  while (ks * rows < dk) ks <<= 1;          // row groups: a power of two, at most 32
+  while (ks * rows < dk) ks <<= 1;          // row groups: a power of two, at most 16
   const int cols_per_block = (32 / ks) * SCAN_WARPS;
   const int slices = (dv + cols_per_block - 1) / cols_per_block;
   const int esize = dtype == DT_F32 ? 4 : 2;
   const int token_bytes = (2 * dk + cols_per_block) * esize + (per_channel ? dk * 4 : 0);
   int chunk = 16;
-  while (chunk > 2 && chunk * token_bytes > 24 * 1024) chunk >>= 1;
-  const size_t smem = 2 * (size_t)(((chunk * (2 * dk + cols_per_block) * esize + 15) & ~15) + (per_channel ? chunk * dk * 4 : 0));
+  while (chunk > 2 && chunk * token_bytes > 16 * 1024) chunk >>= 1;
+  const size_t smem = SCAN_BUFFERS * (size_t)(((chunk * (2 * dk + cols_per_block) * esize + 15) & ~15) + (per_channel ? chunk * dk * 4 : 0));
   LLM_HOST_CHECK(smem <= 200 * 1024, ERR_BAD_SIZE);
   // 16-byte copies need every head slice of every row to start and end on a 16-byte boundary
   const int per = 16 / esize;
@@ -179,17 +238,28 @@ extern "C" int llm_linear_attention_scan(const void* q, const void* k, const voi
   int aligned = ok(q, q_stride) && ok(k, k_stride) && ok(v, v_stride) && dk % per == 0 && dv % per == 0 &&
                 cols_per_block % per == 0 && (!per_channel || (dk % 4 == 0 && ((uintptr_t)decay % 16) == 0));
   dim3 grid(n_seqs, heads, slices);
-#define GO(T, DEC, ROWS)                                                                                         \
-  return scan_launch<T, DEC, ROWS>(grid, smem, stream, q, k, v, q_stride, k_stride, v_stride, decay, state, out, \
-                                   seq_slot, seq_q_start, seq_q_len, heads, dk, dv, ks, chunk, aligned, q_scale)
+  // 16-byte loads of a thread's rows from shared memory: the threads' rows cover the key size exactly, and
+  // the buffers' token stride a multiple of 16 bytes (the aligned copies give the rest)
+  const bool vec = aligned && dk == ks * rows && ((2 * dk + cols_per_block) * esize) % 16 == 0;
+#define GO(T, DEC, ROWS)                                                                                        \
+  do {                                                                                                          \
+    if (vec)                                                                                                    \
+      return scan_launch<T, DEC, ROWS, true>(grid, smem, stream, q, k, v, q_stride, k_stride, v_stride, decay,  \
+                                             state, out, seq_slot, seq_q_start, seq_q_len, heads, dk, dv, ks,   \
+                                             chunk, aligned, q_scale);                                          \
+    return scan_launch<T, DEC, ROWS, false>(grid, smem, stream, q, k, v, q_stride, k_stride, v_stride, decay,   \
+                                            state, out, seq_slot, seq_q_start, seq_q_len, heads, dk, dv, ks,    \
+                                            chunk, aligned, q_scale);                                           \
+  } while (0)
   if (dtype == DT_F32) {
-    if (per_channel) { if (rows == 4) GO(float, 1, 4); else GO(float, 1, 8); }
-    else { if (rows == 4) GO(float, 0, 4); else GO(float, 0, 8); }
+    if (per_channel) { if (rows == 8) GO(float, 1, 8); else GO(float, 1, 16); }
+    else { if (rows == 8) GO(float, 0, 8); else GO(float, 0, 16); }
   } else {
-    if (per_channel) { if (rows == 4) GO(__nv_bfloat16, 1, 4); else GO(__nv_bfloat16, 1, 8); }
-    else { if (rows == 4) GO(__nv_bfloat16, 0, 4); else GO(__nv_bfloat16, 0, 8); }
+    if (per_channel) { if (rows == 8) GO(__nv_bfloat16, 1, 8); else GO(__nv_bfloat16, 1, 16); }
+    else { if (rows == 8) GO(__nv_bfloat16, 0, 8); else GO(__nv_bfloat16, 0, 16); }
   }
 #undef GO
+  return ERR_BAD_SIZE;
 }
 
 // ----------------------------------------------------------------------------- decay gate

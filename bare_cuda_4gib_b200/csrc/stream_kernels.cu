@@ -190,11 +190,37 @@ __global__ void activation_kernel(const TI* in, int n_partials, long long partia
   }
 }
 
+// The same for one bfloat16 matrix in and out (possibly the same one), eight elements at a time:
+// width, both strides and both addresses multiples of eight elements.
+__global__ void activation_bf16x8_kernel(const __nv_bfloat16* in, long long in_stride, __nv_bfloat16* out,
+                                         long long out_stride, int rows, int width8, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c8 >= width8) return;
+  for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+    uint4 raw = *reinterpret_cast<const uint4*>(in + (long long)r * in_stride + c8 * 8);
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      h[j] = __floats2bfloat162_rn(activate(__low2float(h[j]), kind), activate(__high2float(h[j]), kind));
+    *reinterpret_cast<uint4*>(out + (long long)r * out_stride + c8 * 8) = raw;
+  }
+}
+
 extern "C" int llm_activation(const void* in, int in_dtype, int n_partials, long long partial_stride,
                               long long in_stride, void* out, int out_dtype, long long out_stride, int rows, int width,
                               int kind, cudaStream_t stream) {
   if (rows <= 0 || width <= 0) return 0;
   LLM_HOST_CHECK(kind >= 0 && kind <= 3, ERR_BAD_SIZE);
+  if (in_dtype == DT_BF16 && out_dtype == DT_BF16 && n_partials == 1 && width % 8 == 0 && in_stride % 8 == 0 &&
+      out_stride % 8 == 0 && ((uintptr_t)in % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+    const int width8 = width / 8;
+    dim3 grid((width8 + 127) / 128, rows < 2048 ? rows : 2048);
+    launch_kernel(activation_bf16x8_kernel, grid, 128, 0, stream, (const __nv_bfloat16*)in, in_stride,
+                  (__nv_bfloat16*)out, out_stride, rows, width8, kind);
+    return launch_status();
+  }
   const long long total = (long long)rows * width;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);

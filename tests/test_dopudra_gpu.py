@@ -244,3 +244,61 @@ def test_greedy_generation_through_the_engine(name):
             best = int(row.argmax())
             if token != best:        # a tie within float32 rounding may go either way
                 assert float(row[best] - row[token]) < 1e-4 * float(row.abs().max()), (i, token, best)
+
+
+# ------------------------------------------------------------------------- command line tools
+
+def _tool(tool, *args, feed=None):
+    import os
+    import pathlib
+    import subprocess
+    import sys
+
+    root = pathlib.Path(__file__).resolve().parents[1]
+    done = subprocess.run([sys.executable, str(root / "bin" / tool), *map(str, args)], input=feed, capture_output=True,
+                          text=True, env=dict(os.environ, PYTHONDONTWRITEBYTECODE="1"), timeout=900)
+    assert done.returncode == 0, done.stderr[-2000:]
+    return done.stdout
+
+
+def test_llm_infer_prints_the_plain_greedy_tokens():
+    folder = D.model_folder("Y")
+    prompt = [5, 17, 3, 100, 9, 41, 77]
+    out = _tool("llm-infer", "--model", folder, "--prompt", ",".join(map(str, prompt)), "--tokens", 10, "--dtype",
+                "float32", "--page-tokens", 32)
+    generated = [int(t) for t in out.split("generated:")[1].split()]
+    assert len(generated) == 10
+    logits = D.plain_logits(folder, prompt + generated[:-1])
+    assert generated == [int(logits[len(prompt) - 1 + i].argmax()) for i in range(10)]
+    assert out.splitlines()[0].startswith("[llm] 3 layers, hidden 96, vocab 130")
+
+
+def test_llm_infer_runs_a_preset_with_random_weights(tmp_path):
+    out = _tool("llm-infer", "--model", tmp_path / "m", "--random", "dopudra-tiny", "--prompt", "1,2,3", "--tokens", 5)
+    assert len(out.split("generated:")[1].split()) == 5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_replay_tool(dtype, tmp_path):
+    """bin/trace_run on two requests that share steps; the second takes the first one's slot and pages."""
+    import json
+    import numpy as np
+
+    folder = D.model_folder("X")
+    requests = _requests("X", 17, [40, 19, 33])
+    a, b, c = requests["r0"], requests["r1"], requests["r2"]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}, {"id": "b", "tokens": b[:2], "want": [1]}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": b[2:], "want": [16]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[30:39], "want": []}, {"id": "c", "tokens": c, "want": [32]}], "end": ["c"]},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[39:], "want": [0]}], "end": ["a"]}]
+    out = tmp_path / "out"
+    printed = _tool("trace_run", "--model", folder, "--dtype", dtype, "--out", out, "--max-tokens", 128, "--page-tokens", 16,
+                    feed="".join(json.dumps(s) + "\n" for s in steps))
+    assert [l for l in printed.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+    want = {0: [("r0", 0), ("r0", 29), ("r1", 1)], 1: [("r1", 18)], 2: [("r2", 32)], 3: [("r0", 39)]}
+    vocab = D.CONFIGS["X"][0]["vocab"]
+    for step, rows in want.items():
+        got = torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(len(rows), vocab).copy())
+        for i, (rid, p) in enumerate(rows):
+            err = H.row_error(got[i], D.plain_logits(folder, requests[rid])[p])
+            assert err <= D.TOLERANCE[dtype], (step, rid, p, err)

@@ -72,13 +72,17 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
                              float* __restrict__ out,                  // [tokens][heads * dv]
                              const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_q_start,
                              const int32_t* __restrict__ seq_q_len, int heads, int dk, int dv, int ks, int chunk,
-                             int aligned, float q_scale) {
+                             int aligned, float q_scale, int seg_len, int n_segs, int slices,
+                             float* __restrict__ seg_state,      // [sequences][n_segs][heads][dk][dv]
+                             float* __restrict__ seg_decay,      // [sequences][n_segs][heads][dk]
+                             float* __restrict__ cum) {          // [tokens][heads * dk]
   pdl_launch_dependents();
   extern __shared__ __align__(16) uint8_t scan_smem[];
   const int seq = blockIdx.x, head = blockIdx.y;
+  const int seg = blockIdx.z / slices;      // with n_segs > 1: which stretch of seg_len tokens (see scan_carry_kernel)
   const int cols_per_warp = 32 / ks;
   const int cols_per_block = cols_per_warp * SCAN_WARPS;
-  const int col0 = blockIdx.z * cols_per_block;
+  const int col0 = (blockIdx.z % slices) * cols_per_block;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int kr = lane % ks;
   const int my_col = warp * cols_per_warp + lane / ks;
@@ -89,17 +93,25 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
   const int t_bytes = (chunk * tok * (int)sizeof(T) + 15) & ~15;
   const int buf_bytes = t_bytes + (DECAY == DECAY_PER_CHANNEL ? chunk * dk * 4 : 0);
   pdl_wait();
-  const int n = seq_q_len[seq];
-  if (n <= 0) return;
-  const int row0 = seq_q_start[seq];
+  const int n_all = seq_q_len[seq];
+  const int seg_first = n_segs > 1 ? seg * seg_len : 0;
+  if (n_all <= seg_first) return;
+  const int n = n_segs > 1 ? min(seg_len, n_all - seg_first) : n_all;
+  const int row0 = seq_q_start[seq] + seg_first;
   const int slot = seq_slot[seq];
   float* S_g = state + (((long long)slot * heads + head) * dk) * dv;
   float S[ROWS];
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
     const int i = kr * ROWS + r;
-    S[r] = (live && i < dk) ? S_g[(long long)i * dv + col] : 0.0f;
+    S[r] = (live && i < dk && seg == 0) ? S_g[(long long)i * dv + col] : 0.0f;   // later stretches start from nothing
   }
+  // a later stretch also leaves, per token, the product of the decays from its start (one thread group
+  // per head does: the first value column's)
+  const bool keeps_cum = DECAY == DECAY_PER_CHANNEL && n_segs > 1 && seg > 0 && col == 0;
+  float cp[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) cp[r] = 1.0f;
   const int valid = min(ROWS, dk - kr * ROWS);     // rows of this thread inside the key size (may be <= 0)
   const float head_decay = DECAY == DECAY_PER_HEAD ? decay[head] : 0.0f;
 
@@ -163,7 +175,17 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
       float qq[ROWS], kk[ROWS], aa[ROWS];
       load_rows<T, ROWS, VEC>(w + at, valid, qq);
       load_rows<T, ROWS, VEC>(w + dk + at, valid, kk);
-      if (DECAY == DECAY_PER_CHANNEL) load_rows<float, ROWS, VEC>(dec + t * dk + at, valid, aa);
+      if (DECAY == DECAY_PER_CHANNEL) {
+        load_rows<float, ROWS, VEC>(dec + t * dk + at, valid, aa);
+        if (keeps_cum) {
+          float* c_row = cum + (long long)(row0 + first + t) * ((long long)heads * dk) + head * dk + kr * ROWS;
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r) {
+            cp[r] *= aa[r];
+            if (r < valid) c_row[r] = cp[r];
+          }
+        }
+      }
       float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) {
@@ -193,6 +215,15 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
       if (live && kr == 0) o_row[(long long)t0 * ((long long)heads * dv)] = acc * q_scale;
     }
   }
+  if (n_segs > 1) {
+    S_g = seg_state + ((((long long)seq * n_segs + seg) * heads + head) * dk) * dv;
+    if (keeps_cum) {
+      float* d_row = seg_decay + (((long long)seq * n_segs + seg) * heads + head) * dk + kr * ROWS;
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r)
+        if (r < valid) d_row[r] = cp[r];
+    }
+  }
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
     const int i = kr * ROWS + r;
@@ -200,16 +231,133 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
   }
 }
 
+// A long portion is walked as n_segs stretches of seg_len tokens side by side: stretch 0 from the
+// request's state, the others from nothing.  With D_p the product of the decays over stretch p and
+// E_p the state stretch p ends with, the state the request really has at the start of stretch p is
+//   C_0 = state,   C_(p+1) = D_p C_p + E_p   (E_0 already contains C_0),
+// and token t of stretch p >= 1 misses (c_t q_t)^T C_p in its output, c_t the product of the decays
+// from the stretch's start to t.  This kernel walks p in order per (request, head): it leaves C_p in
+// place of E_(p-1) and the final state in the request's slot.
+template <int DECAY>
+__global__ void scan_carry_kernel(float* __restrict__ state, float* __restrict__ seg_state,
+                                  const float* __restrict__ seg_decay, const float* __restrict__ decay,
+                                  const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_q_len,
+                                  int heads, int dk, int dv, int seg_len, int n_segs) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seq = blockIdx.x, head = blockIdx.y;
+  const int n = seq_q_len[seq];
+  if (n <= 0) return;
+  const int used = (n + seg_len - 1) / seg_len;
+  float* S_g = state + (((long long)seq_slot[seq] * heads + head) * dk) * dv;
+  const long long per = (long long)dk * dv;
+  float* E = seg_state + (((long long)seq * n_segs) * heads + head) * per;      // stretch p at E + p * heads * per
+  const float lam = DECAY == DECAY_PER_HEAD ? decay[head] : 0.0f;
+  // every state element walks the stretches by itself: one per thread, blockIdx.z times blockDim.x apart
+  for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < dk * dv; e += gridDim.z * blockDim.x) {
+    const int i = e / dv;
+    float S = E[e];
+#pragma unroll 4
+    for (int p = 1; p < used; ++p) {
+      float* Ep = E + (long long)p * heads * per;
+      const int len = min(seg_len, n - p * seg_len);
+      const float d = DECAY == DECAY_PER_HEAD
+                          ? powf(lam, (float)len)
+                          : seg_decay[(((long long)seq * n_segs + p) * heads + head) * dk + i];
+      const float mine = Ep[e];
+      Ep[e - (long long)heads * per] = S;      // C_p, where E_(p-1) was
+      S = d * S + mine;
+    }
+    S_g[e] = S;
+  }
+}
+
+#define CORRECT_TOKENS 32
+#define CORRECT_THREADS 128
+
+// out[t] += ((c_t q_t)^T C_p) * q_scale for the tokens of stretches p >= 1.  A block takes
+// CORRECT_TOKENS tokens of one stretch and one head: C_p and the scaled queries in shared memory.
+template <typename T, int DECAY>
+__global__ void __launch_bounds__(CORRECT_THREADS)
+scan_correct_kernel(const T* __restrict__ q, long long q_stride, const float* __restrict__ decay,
+                    const float* __restrict__ cum, const float* __restrict__ seg_state, float* __restrict__ out,
+                    const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_q_len, int heads, int dk,
+                    int dv, int seg_len, int n_segs, float q_scale) {
+  pdl_launch_dependents();
+  extern __shared__ float cs[];        // [dk][dv] then [CORRECT_TOKENS][dk]
+  float* qs = cs + dk * dv;
+  pdl_wait();
+  const int seq = blockIdx.z, head = blockIdx.y;
+  const int first = blockIdx.x * CORRECT_TOKENS;      // seg_len is a multiple of CORRECT_TOKENS
+  const int n = seq_q_len[seq];
+  const int p = first / seg_len;
+  if (p == 0 || first >= n) return;
+  const int count = min(CORRECT_TOKENS, n - first);
+  const long long row0 = seq_q_start[seq] + first;
+  const float* C = seg_state + ((((long long)seq * n_segs + (p - 1)) * heads + head) * dk) * dv;
+  for (int e = threadIdx.x; e < dk * dv; e += CORRECT_THREADS) cs[e] = C[e];
+  const float lam = DECAY == DECAY_PER_HEAD ? decay[head] : 0.0f;
+  for (int e = count * dk + threadIdx.x; e < CORRECT_TOKENS * dk; e += CORRECT_THREADS) qs[e] = 0.0f;
+  for (int e = threadIdx.x; e < count * dk; e += CORRECT_THREADS) {
+    const int t = e / dk, i = e - t * dk;
+    const float c = DECAY == DECAY_PER_HEAD ? powf(lam, (float)(first + t - p * seg_len + 1))
+                                            : cum[(row0 + t) * ((long long)heads * dk) + head * dk + i];
+    qs[e] = to_float(q[(row0 + t) * q_stride + head * dk + i]) * c;
+  }
+  __syncthreads();
+  // a thread takes 4 tokens x 4 neighbouring value columns: per key channel four numbers of the
+  // scaled queries and one 16-byte piece of C_p feed sixteen multiply-adds
+  const int col_groups = (dv + 3) / 4;
+  const bool vec = (dv & 3) == 0;
+  for (int tile = threadIdx.x; tile < (CORRECT_TOKENS / 4) * col_groups; tile += CORRECT_THREADS) {
+    const int cg = tile % col_groups, tg = tile / col_groups;
+    if (tg * 4 >= count) continue;
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[a][c] = 0.0f;
+    const float* q0 = qs + (tg * 4) * dk;
+    for (int i = 0; i < dk; ++i) {
+      float cv[4];
+      if (vec) {
+        const float4 x = *reinterpret_cast<const float4*>(cs + i * dv + cg * 4);
+        cv[0] = x.x; cv[1] = x.y; cv[2] = x.z; cv[3] = x.w;
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) cv[c] = cg * 4 + c < dv ? cs[i * dv + cg * 4 + c] : 0.0f;
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const float qv = q0[a * dk + i];      // rows past `count` are zero and never stored
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[a][c] += qv * cv[c];
+      }
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const int t = tg * 4 + a;
+      if (t >= count) continue;
+      float* o = out + (row0 + t) * ((long long)heads * dv) + head * dv + cg * 4;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (cg * 4 + c < dv) o[c] += acc[a][c] * q_scale;
+    }
+  }
+}
+
 template <typename T, int DECAY, int ROWS, bool VEC>
 static int scan_launch(dim3 grid, size_t smem, cudaStream_t stream, const void* q, const void* k, const void* v,
                        long long q_stride, long long k_stride, long long v_stride, const float* decay, float* state,
                        float* out, const int32_t* seq_slot, const int32_t* seq_q_start, const int32_t* seq_q_len,
-                       int heads, int dk, int dv, int ks, int chunk, int aligned, float q_scale) {
+                       int heads, int dk, int dv, int ks, int chunk, int aligned, float q_scale, int seg_len, int n_segs,
+                       int slices, float* seg_state, float* seg_decay, float* cum) {
   auto kern = linear_attention_scan_kernel<T, DECAY, ROWS, VEC>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return launch_status();
   launch_kernel(kern, grid, SCAN_THREADS, smem, stream, (const T*)q, (const T*)k, (const T*)v, q_stride, k_stride,
-                v_stride, decay, state, out, seq_slot, seq_q_start, seq_q_len, heads, dk, dv, ks, chunk, aligned, q_scale);
+                v_stride, decay, state, out, seq_slot, seq_q_start, seq_q_len, heads, dk, dv, ks, chunk, aligned, q_scale,
+                seg_len, n_segs, slices, seg_state, seg_decay, cum);
   return launch_status();
 }
 
@@ -217,8 +365,11 @@ extern "C" int llm_linear_attention_scan(const void* q, const void* k, const voi
                                          long long k_stride, long long v_stride, const float* decay, int per_channel,
                                          float* state, float* out, const int32_t* seq_slot,
                                          const int32_t* seq_q_start, const int32_t* seq_q_len, int n_seqs, int heads,
-                                         int dk, int dv, float q_scale, cudaStream_t stream) {
+                                         int dk, int dv, float q_scale, int seg_len, int n_segs, float* seg_state,
+                                         float* seg_decay, float* cum, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
+  LLM_HOST_CHECK(n_segs >= 1 && (n_segs == 1 || (seg_len > 0 && seg_len % CORRECT_TOKENS == 0 && seg_state &&
+                                                 (!per_channel || (seg_decay && cum)))), ERR_BAD_SIZE);
   LLM_HOST_CHECK(dk >= 1 && dk <= 256 && dv >= 1 && heads >= 1 && heads <= 65535, ERR_BAD_SIZE);
   LLM_HOST_CHECK(dtype == DT_F32 || dtype == DT_BF16, ERR_BAD_DTYPE);
   const int rows = dk <= 32 ? 8 : 16;
@@ -237,7 +388,8 @@ extern "C" int llm_linear_attention_scan(const void* q, const void* k, const voi
   auto ok = [&](const void* p, long long stride) { return ((uintptr_t)p % 16) == 0 && stride % per == 0; };
   int aligned = ok(q, q_stride) && ok(k, k_stride) && ok(v, v_stride) && dk % per == 0 && dv % per == 0 &&
                 cols_per_block % per == 0 && (!per_channel || (dk % 4 == 0 && ((uintptr_t)decay % 16) == 0));
-  dim3 grid(n_seqs, heads, slices);
+  dim3 grid(n_seqs, heads, slices * n_segs);
+  LLM_HOST_CHECK(grid.z <= 65535, ERR_BAD_SIZE);
   // 16-byte loads of a thread's rows from shared memory: the threads' rows cover the key size exactly, and
   // the buffers' token stride a multiple of 16 bytes (the aligned copies give the rest)
   const bool vec = aligned && dk == ks * rows && ((2 * dk + cols_per_block) * esize) % 16 == 0;
@@ -246,10 +398,10 @@ extern "C" int llm_linear_attention_scan(const void* q, const void* k, const voi
     if (vec)                                                                                                    \
       return scan_launch<T, DEC, ROWS, true>(grid, smem, stream, q, k, v, q_stride, k_stride, v_stride, decay,  \
                                              state, out, seq_slot, seq_q_start, seq_q_len, heads, dk, dv, ks,   \
-                                             chunk, aligned, q_scale);                                          \
+                                             chunk, aligned, q_scale, seg_len, n_segs, slices, seg_state, seg_decay, cum); \
     return scan_launch<T, DEC, ROWS, false>(grid, smem, stream, q, k, v, q_stride, k_stride, v_stride, decay,   \
                                             state, out, seq_slot, seq_q_start, seq_q_len, heads, dk, dv, ks,    \
-                                            chunk, aligned, q_scale);                                           \
+                                            chunk, aligned, q_scale, seg_len, n_segs, slices, seg_state, seg_decay, cum); \
   } while (0)
   if (dtype == DT_F32) {
     if (per_channel) { if (rows == 8) GO(float, 1, 8); else GO(float, 1, 16); }
@@ -260,6 +412,42 @@ extern "C" int llm_linear_attention_scan(const void* q, const void* k, const voi
   }
 #undef GO
   return ERR_BAD_SIZE;
+}
+
+// After a scan in n_segs > 1 stretches: the states the stretches really start from, the request's
+// final state, and what the later stretches' outputs miss.  `max_q_len`: the longest portion.
+extern "C" int llm_linear_attention_join(const void* q, int dtype, long long q_stride, const float* decay,
+                                         int per_channel, float* state, float* out, const int32_t* seq_slot,
+                                         const int32_t* seq_q_start, const int32_t* seq_q_len, int n_seqs, int heads,
+                                         int dk, int dv, float q_scale, int seg_len, int n_segs, int max_q_len,
+                                         float* seg_state, const float* seg_decay, const float* cum,
+                                         cudaStream_t stream) {
+  if (n_seqs <= 0 || n_segs <= 1) return 0;
+  LLM_HOST_CHECK(seg_len > 0 && seg_len % CORRECT_TOKENS == 0 && n_seqs <= 65535 && heads <= 65535, ERR_BAD_SIZE);
+  dim3 carry_grid(n_seqs, heads, (dk * dv + 1023) / 1024);
+  if (per_channel)
+    launch_kernel(scan_carry_kernel<1>, carry_grid, 256, 0, stream, state, seg_state, seg_decay, decay, seq_slot,
+                  seq_q_len, heads, dk, dv, seg_len, n_segs);
+  else
+    launch_kernel(scan_carry_kernel<0>, carry_grid, 256, 0, stream, state, seg_state, seg_decay, decay, seq_slot,
+                  seq_q_len, heads, dk, dv, seg_len, n_segs);
+  int status = launch_status();
+  if (status) return status;
+  const size_t smem = ((size_t)dk * dv + (size_t)CORRECT_TOKENS * dk) * sizeof(float);
+  LLM_HOST_CHECK(smem <= 200 * 1024, ERR_BAD_SIZE);
+  dim3 grid((max_q_len + CORRECT_TOKENS - 1) / CORRECT_TOKENS, heads, n_seqs);
+#define GO(T, DEC)                                                                                                  \
+  do {                                                                                                              \
+    if (smem > 48 * 1024)                                                                                           \
+      cudaFuncSetAttribute(scan_correct_kernel<T, DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+    launch_kernel(scan_correct_kernel<T, DEC>, grid, CORRECT_THREADS, smem, stream, (const T*)q, q_stride, decay, cum, \
+                  seg_state, out, seq_q_start, seq_q_len, heads, dk, dv, seg_len, n_segs, q_scale);                  \
+  } while (0)
+  if (dtype == DT_F32) { if (per_channel) GO(float, 1); else GO(float, 0); }
+  else if (dtype == DT_BF16) { if (per_channel) GO(__nv_bfloat16, 1); else GO(__nv_bfloat16, 0); }
+  else return ERR_BAD_DTYPE;
+#undef GO
+  return launch_status();
 }
 
 // ----------------------------------------------------------------------------- decay gate

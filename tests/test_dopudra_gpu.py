@@ -302,3 +302,33 @@ def test_trace_replay_tool(dtype, tmp_path):
         for i, (rid, p) in enumerate(rows):
             err = H.row_error(got[i], D.plain_logits(folder, requests[rid])[p])
             assert err <= D.TOLERANCE[dtype], (step, rid, p, err)
+
+
+# ------------------------------------------------------------ long portions walked in stretches
+
+@pytest.mark.parametrize("rank", [8, 5])      # 5: the projection's rows are not 16-byte aligned
+def test_long_portions_walked_in_stretches(rank, monkeypatch):
+    """A bfloat16 step whose portions are several hundred tokens long walks the linear-attention
+    states in stretches side by side and joins them: the same logits as one walk, and the plain
+    implementation's; two requests of different length in one step, the second carried on."""
+    from bare_cuda_4gib_b200.kernels import linear_attention as LA
+
+    layers = [D.lightning(2, 16, 16, [1.0, 0.9]),
+              D.parallel(D.left(2, 1, 16, 16, 3, 0.25, 300, 0.2, 50), D.right(2, 64, 8, 4.0), 0.8, 1.2, ff=48)]
+    cfg = dict(copy.deepcopy(D.CFG_Y), layers=layers, streams=2, max_positions=704)
+    folder = H.tmp_root() / f"dopudra-stretches-{rank}"
+    D.register(folder, cfg, D.random_tensors(cfg, rank, 12, 41))
+    rng = random.Random(3)
+    a, b = H.random_ids(rng, 700, cfg["vocab"]), H.random_ids(rng, 640, cfg["vocab"])
+    tail = lambda n, k=24: list(range(n - k, n))
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:650], "want": [0, 127, 128, 129, 255, 256, 400] + tail(650)},
+                                     {"id": "b", "tokens": b[:2], "want": [1]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[650:], "want": tail(50, 10)},
+                                     {"id": "b", "tokens": b[2:], "want": [0, 125, 126, 127, 300] + tail(638)}], "end": ["a", "b"]}]
+    cut = H.Replayer(folder, "bfloat16", 64, 1408).run(steps)
+    monkeypatch.setattr(LA, "STRETCHES_FROM", 1 << 30)
+    whole = H.Replayer(folder, "bfloat16", 64, 1408).run(steps)
+    assert sorted(cut) == sorted(whole)
+    for key in cut:
+        assert H.row_error(cut[key], whole[key]) < 1e-2, key
+    D.check(folder, {"a": a, "b": b}, cut, "bfloat16", expect_all=False)

@@ -119,6 +119,91 @@ __global__ void __launch_bounds__(256) stream_step_kernel(float* __restrict__ st
   for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_float<TO>(u_row[i] * scale * weight[i]);
 }
 
+// The same with four neighbouring channels per thread and 16-byte accesses: width a multiple of 4,
+// float32 partial results, every row 16-byte aligned.
+__device__ __forceinline__ float4 f4_scale_add(float4 acc, float s, float4 x) {
+  acc.x += s * x.x; acc.y += s * x.y; acc.z += s * x.z; acc.w += s * x.w;
+  return acc;
+}
+
+template <typename TO, int SMAX>
+__global__ void __launch_bounds__(256) stream_step_vec_kernel(float* __restrict__ streams_buf, int n_streams,
+                                   const float* __restrict__ delta, int n_partials, long long partial_stride,
+                                   long long delta_row_stride, const float* __restrict__ delta_scale,
+                                   const float* __restrict__ write_vec, const float* __restrict__ mix,
+                                   const float* __restrict__ read_vec, const float* __restrict__ weight,
+                                   TO* __restrict__ out, const int32_t* __restrict__ row_index, int width, float eps) {
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) float smem[];
+  float4* u_row = reinterpret_cast<float4*>(smem);
+  float* scratch = smem + width;
+  float* s_mix = scratch + 32;
+  float* s_write = s_mix + MAX_STREAMS * MAX_STREAMS;
+  float* s_read = s_write + MAX_STREAMS;
+  const int S = n_streams;
+  for (int i = threadIdx.x; i < S * S; i += blockDim.x) s_mix[i] = mix ? mix[i] : ((i / S) == (i % S) ? 1.0f : 0.0f);
+  for (int i = threadIdx.x; i < S; i += blockDim.x) {
+    s_write[i] = write_vec ? write_vec[i] : 1.0f;
+    s_read[i] = read_vec ? read_vec[i] : 1.0f;
+  }
+  pdl_wait();
+  __syncthreads();
+  const int r = blockIdx.x;
+  const long long src = row_index ? row_index[r] : r;
+  const int w4 = width / 4;
+  float4* x = reinterpret_cast<float4*>(streams_buf + src * S * width);
+  float sq = 0.0f;
+  for (int i = threadIdx.x; i < w4; i += blockDim.x) {
+    float4 xs[SMAX];
+#pragma unroll
+    for (int s = 0; s < SMAX; ++s)
+      if (s < S) xs[s] = x[(long long)s * w4 + i];
+    float4 u = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (delta) {
+      float4 y = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      for (int p = 0; p < n_partials; ++p)
+        y = f4_scale_add(y, 1.0f, reinterpret_cast<const float4*>(delta + p * partial_stride + src * delta_row_stride)[i]);
+      if (delta_scale) {
+        const float4 g = reinterpret_cast<const float4*>(delta_scale)[i];
+        y.x *= g.x; y.y *= g.y; y.z *= g.z; y.w *= g.w;
+      }
+#pragma unroll
+      for (int t = 0; t < SMAX; ++t) {
+        if (t < S) {
+          float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+          for (int s = 0; s < SMAX; ++s)
+            if (s < S) v = f4_scale_add(v, s_mix[s * S + t], xs[s]);
+          v = f4_scale_add(v, s_write[t], y);
+          x[(long long)t * w4 + i] = v;
+          u = f4_scale_add(u, s_read[t], v);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < SMAX; ++t)
+        if (t < S) u = f4_scale_add(u, s_read[t], xs[t]);
+    }
+    u_row[i] = u;
+    sq += u.x * u.x;
+    sq += u.y * u.y;
+    sq += u.z * u.z;
+    sq += u.w * u.w;
+  }
+  if (!out) return;
+  const float total = block_sum(sq, scratch);
+  const float scale = 1.0f / sqrtf(total / (float)width + eps);
+  TO* dst = out + (long long)r * width;
+  for (int i = threadIdx.x; i < w4; i += blockDim.x) {
+    const float4 u = u_row[i];
+    const float4 g = reinterpret_cast<const float4*>(weight)[i];
+    dst[4 * i] = from_float<TO>(u.x * scale * g.x);
+    dst[4 * i + 1] = from_float<TO>(u.y * scale * g.y);
+    dst[4 * i + 2] = from_float<TO>(u.z * scale * g.z);
+    dst[4 * i + 3] = from_float<TO>(u.w * scale * g.w);
+  }
+}
+
 extern "C" int llm_stream_step(float* streams_buf, int n_streams, const void* delta, int delta_dtype, int n_partials,
                                long long partial_stride, long long delta_row_stride, const float* delta_scale,
                                const float* write_vec, const float* mix, const float* read_vec, const float* weight,
@@ -138,6 +223,25 @@ extern "C" int llm_stream_step(float* streams_buf, int n_streams, const void* de
                   (const TD*)delta, n_partials, partial_stride, delta_row_stride, delta_scale, write_vec, mix,  \
                   read_vec, weight, (TO*)out, row_index, width, eps);                                          \
   } while (0)
+  // four channels per thread where everything is 16-byte aligned and the partial results are float32
+  auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  const bool vec = width % 4 == 0 && n_streams <= 4 && (!delta || (delta_dtype == DT_F32 && al(delta) &&
+                   partial_stride % 4 == 0 && delta_row_stride % 4 == 0)) && al(streams_buf) && al(delta_scale) &&
+                   al(weight) && al(out);
+#define LAUNCH_V(TO, SMAX)                                                                                     \
+  launch_kernel(stream_step_vec_kernel<TO, SMAX>, rows, width >= 2048 ? 256 : 128, smem, stream, streams_buf,  \
+                n_streams, (const float*)delta, n_partials, partial_stride, delta_row_stride, delta_scale,     \
+                write_vec, mix, read_vec, weight, (TO*)out, row_index, width, eps)
+  if (vec && smem <= 48 * 1024 && (out_dtype == DT_F32 || out_dtype == DT_BF16)) {
+    if (out_dtype == DT_F32) {
+      if (n_streams == 1) LAUNCH_V(float, 1); else if (n_streams == 2) LAUNCH_V(float, 2); else LAUNCH_V(float, 4);
+    } else {
+      if (n_streams == 1) LAUNCH_V(__nv_bfloat16, 1); else if (n_streams == 2) LAUNCH_V(__nv_bfloat16, 2);
+      else LAUNCH_V(__nv_bfloat16, 4);
+    }
+    return launch_status();
+  }
+#undef LAUNCH_V
 #define LAUNCH(TD, TO)                                     \
   do {                                                     \
     if (n_streams == 1) LAUNCH_S(TD, TO, 1);               \

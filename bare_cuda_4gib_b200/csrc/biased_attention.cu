@@ -60,8 +60,15 @@ __global__ void __launch_bounds__(512) conv_norm_cache_kernel(const T* __restric
   const int hist = taps - 1;
   const float* ring_slot = ring + (long long)slot * (hist > 0 ? hist : 1) * C;
   float sq_q = 0.0f, sq_k = 0.0f;
+  // most rows of a prompt's portion have all their taps inside the step's own rows: no case per tap
+  const bool inside = p - hist >= p0;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     float y = 0.0f;
+    if (inside) {
+      const T* col = u + (long long)(t - hist) * u_stride + c;
+      const float* w = conv_w + (long long)c * taps;
+      for (int j = 0; j < taps; ++j) y += w[j] * to_float(col[(long long)j * u_stride]);
+    } else
     for (int j = 0; j < taps; ++j) {
       const int x = p - hist + j;
       if (x < 0) continue;

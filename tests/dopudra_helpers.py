@@ -164,3 +164,12 @@ def check(folder, requests: Dict[str, List[int]], got, dtype: str, expect_all: b
         for p in places:
             err = H.row_error(got[(rid, p)], want[p])
             assert err <= TOLERANCE[dtype], f"request {rid} position {p} of {len(ids)}: error {err:.3e}"
+
+
+def check_most(folder, requests: Dict[str, List[int]], got, dtype: str, share: float = 0.95, worst: float = 0.5) -> None:
+    """For configurations drawn at random in bfloat16, where single positions can be ill-conditioned (see
+    TOLERANCE): `share` of the rows within the tolerance, none beyond `worst`."""
+    errors = sorted(H.row_error(got[(rid, p)], plain_logits(folder, requests[rid])[p]) for (rid, p) in got)
+    assert errors[-1] <= worst, f"worst row: error {errors[-1]:.3e}"
+    at = min(len(errors) - 1, int(share * len(errors)))
+    assert errors[at] <= TOLERANCE[dtype], f"{share:.0%} of the rows: error {errors[at]:.3e}"

@@ -332,3 +332,57 @@ def test_long_portions_walked_in_stretches(rank, monkeypatch):
     for key in cut:
         assert H.row_error(cut[key], whole[key]) < 1e-2, key
     D.check(folder, {"a": a, "b": b}, cut, "bfloat16", expect_all=False)
+
+
+# ----------------------------------------------------------------- configurations drawn at random
+
+def _random_config(seed):
+    rng = random.Random(seed)
+    pick = rng.choice
+    width = pick([40, 64, 72, 100, 128, 136])
+    streams = pick([1, 2, 3, 4, 6])
+
+    def ff():
+        return pick([None, pick([24, 50, 96, 160])])
+
+    def light():
+        heads = pick([1, 2, 3, 5])
+        return D.lightning(heads, pick([4, 8, 12, 16, 32, 40, 64]), pick([4, 8, 10, 16, 24, 64]),
+                           [pick([1.0, 0.999, 0.9, 0.5, 0.0]) for _ in range(heads)], ff=ff())
+
+    def both():
+        kv = pick([1, 2, 3])
+        heads = kv * pick([1, 2, 4])
+        dim = pick([8, 12, 16, 32, 48, 64])
+        vdim = pick([dim, dim, pick([8, 16, 20, 40])])
+        l = D.left(heads, kv, dim, vdim, pick([1, 2, 3, 4, 6]), pick([0.1, 0.3, dim ** -0.5]), pick([6, 30, 64, 500]),
+                   pick([0.0, 0.25, 1.0]), pick([1, 3, 16, 64]))
+        r = D.right(pick([1, 2, 4]), pick([4, 8, 16, 24, 64]), pick([4, 8, 16, 32]), pick([1.0, 2.0, 16.0]))
+        return D.parallel(l, r, pick([0.5, 1.0, 1.2]), pick([0.7, 1.0, 1.1]), ff=ff())
+
+    layers = [pick([light, both])() for _ in range(rng.randrange(1, 5))]
+    cfg = {"architecture": "Dopudra", "vocab": pick([50, 97, 301]), "width": width, "max_positions": 128, "streams": streams,
+           "embedding": {"scale": pick([0.5, 1.0, 3.0])}, "norm": {"eps": pick([1e-6, 1e-5])}, "layers": layers}
+    return cfg, pick([3, 4, 8, 16]), pick([2, 6, 8, 16, 32])
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_configurations_drawn_at_random(seed):
+    cfg, rank, rows = _random_config(100 + seed)
+    folder = H.tmp_root() / f"dopudra-random-{seed}"
+    D.register(folder, cfg, D.random_tensors(cfg, rank, rows, seed))
+    rng = random.Random(seed)
+    requests = {"a": H.random_ids(rng, 70, cfg["vocab"]), "b": H.random_ids(rng, 33, cfg["vocab"]),
+                "c": H.random_ids(rng, 9, cfg["vocab"])}
+    page = rng.choice([16, 32, 64])
+    steps = H.trace_mixed(requests, random.Random(seed), live=2, budget_tokens=256, page=page)
+    got = H.Replayer(folder, "float32", page, 256, max_live=2, shuffle_seed=seed).run(steps)
+    D.check(folder, requests, got, "float32")
+    # bfloat16: the fast kernels against the plain ones row by row, and both against the plain implementation
+    fast = H.Replayer(folder, "bfloat16", page, 256, max_live=2, shuffle_seed=seed).run(steps)
+    slow = H.Replayer(folder, "bfloat16", page, 256, max_live=2, shuffle_seed=seed, use_fast_gemm=False,
+                      use_fast_attention=False).run(steps)
+    assert sorted(fast) == sorted(slow) and len(fast) == sum(len(ids) for ids in requests.values())
+    agree = sorted(H.row_error(fast[key], slow[key]) for key in fast)
+    assert agree[int(0.95 * len(agree))] <= 2e-2 and agree[-1] <= 0.3, agree[-3:]
+    D.check_most(folder, requests, fast, "bfloat16")

@@ -40,7 +40,7 @@ def _dopudra(width, vocab, positions, streams, blocks, heads, dim, ff, softmax_h
 
 
 PRESETS.update({
-    "dopudra-tiny": _dopudra(64, 300, 256, 2, 1, 2, 16, 96, 2, 1, 32),
+    "dopudra-tiny": _dopudra(64, 300, 512, 2, 1, 2, 16, 96, 2, 1, 32),
     # layer sizes near TinyLlama's (width 2048, feed-forward 5632, 32 heads of 64): 20 layers
     "dopudra-2048": _dopudra(2048, 32000, 4096, 4, 5, 32, 64, 5632, 32, 4, 64),
     # ... and near Llama-2-7B's (width 4096, 32 heads of 128): 32 layers

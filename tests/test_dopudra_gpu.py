@@ -386,3 +386,38 @@ def test_configurations_drawn_at_random(seed):
     agree = sorted(H.row_error(fast[key], slow[key]) for key in fast)
     assert agree[int(0.95 * len(agree))] <= 2e-2 and agree[-1] <= 0.3, agree[-3:]
     D.check_most(folder, requests, fast, "bfloat16")
+
+
+def test_the_other_tools_take_the_design(tmp_path):
+    """llm-bench, llm-ppl and llm-batch-check on a preset with random weights: perplexity against the
+    plain implementation's, the batch check's verdict, the bench tool's table."""
+    import json
+    import math
+
+    import numpy as np
+    from bare_cuda_4gib_b200.weights.safetensors_io import SafetensorsFile
+
+    folder = tmp_path / "m"
+    out = _tool("llm-bench", "--model", folder, "--random", "dopudra-tiny", "--prompt-len", 24, "--tokens", 8, "--runs", 2,
+                "--warmup", 1, "--page-tokens", 16)
+    assert "TTFT" in out and "TPOT" in out
+    rng = random.Random(9)
+    ids = np.array([rng.randrange(300) for _ in range(8200)], dtype="<i4")
+    ids.tofile(tmp_path / "ids.bin")
+    out = _tool("llm-ppl", "--model", folder, "--ids", tmp_path / "ids.bin", "--ctx", 48, "--windows", 2, "--dtype", "float32",
+                "--page-tokens", 16)
+    got = float([l for l in out.splitlines() if l.startswith("perplexity")][0].split()[1])
+    cfg = json.loads((folder / "config.json").read_text())
+    with SafetensorsFile(folder / "model.safetensors") as f:
+        tensors = {name: f.tensor(name) for name in f.entries}
+    nll, n = 0.0, 0
+    for w in range(2):
+        window = [1] + [int(t) for t in ids[w * 47: (w + 1) * 47]]      # the tool puts id 1 before every window
+        logp = torch.log_softmax(P.forward(cfg, tensors, window), -1)
+        for t in range(47):
+            nll -= float(logp[t, window[t + 1]])
+            n += 1
+    assert abs(got - math.exp(nll / n)) <= 1e-3 * math.exp(nll / n), (got, math.exp(nll / n))
+    out = _tool("llm-batch-check", "--model", folder, "--ids", tmp_path / "ids.bin", "--tokens", 12, "--batch", 4,
+                "--page-tokens", 16, "--dtype", "float32")
+    assert "PASS" in out

@@ -37,6 +37,8 @@ def distance_rows(distances: int, rows: int, far: float):
     """For every distance 0 .. distances - 1 the row of a table with `rows` rows: exact up to half
     the table, logarithmic from there to `far`, the last row beyond."""
     half = rows // 2
+    if rows < 1 or (half > 0 and not far > half):
+        raise ConfigError(f"distance bias: a table of {rows} rows needs a far distance above {half}, got {far}")
     out = []
     for n in range(distances):
         if n < half or half == 0:
@@ -82,9 +84,11 @@ class BiasedAttention(BranchMixer):
         f = lambda x: x.to(torch.float32).contiguous()
         self.conv_w = f(torch.cat([t["q_conv"], t["k_conv"], t["v_conv"]], 0))
         self.q_norm_w, self.k_norm_w = f(t["q_norm"]), f(t["k_norm"])
-        rel = f(t["rel"])
+        rel = t["rel"].to(torch.float32).cpu()
         rows = distance_rows(int(self.params["max_positions"]), rel.shape[0], float(self.params["bias_far"]))
-        self.bias = rel[torch.tensor(rows, device=rel.device)].t().contiguous()      # [heads, distances]
+        assert 0 <= min(rows) and max(rows) < rel.shape[0]
+        # gathered on the host (every index checked there), then one copy: [heads, distances]
+        self.bias = rel[torch.tensor(rows)].t().contiguous().to(device)
         # bfloat16 steps with key and value heads of one size the tensor-core kernel is built for run
         # there; everything else (float32, other sizes) runs the plain kernel
         self.fast = None

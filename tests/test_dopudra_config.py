@@ -67,6 +67,8 @@ def test_distance_rows_match_the_plain_buckets():
     from bare_cuda_4gib_b200.parts.biased_attention import distance_rows
     for rows, far in [(16, 240), (7, 50), (9, 9), (32, 128), (2, 5), (16, 20), (5, 1000)]:
         assert distance_rows(600, rows, far) == [P.distance_bucket(n, rows, far) for n in range(600)], (rows, far)
+    with pytest.raises(ConfigError):      # the logarithmic part needs a far distance beyond the exact part
+        distance_rows(600, 16, 6)
 
 
 def test_value_heads_of_their_own_size_in_the_cache():

@@ -16,7 +16,7 @@
 
 #include <math.h>
 
-#define SCAN_WARPS 2
+#define SCAN_WARPS 8
 #define SCAN_THREADS (SCAN_WARPS * 32)
 #define SCAN_BUFFERS 4     // chunks in shared memory: one being walked, the others on their way
 

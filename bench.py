@@ -279,7 +279,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
-    ap.add_argument("--prefill-tokens", type=int, default=2048, help="tokens of the timed prefill step (the contract's figure is 2,048)")
+    ap.add_argument("--prefill-tokens", type=int, default=2048, help="tokens of the timed prefill step (default 2,048)")
     ap.add_argument("--preset", default="tinyllama")
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the preset has (0 = all)")
     ap.add_argument("--repeats", type=int, default=5, help="times every timed region is run (the median is reported)")

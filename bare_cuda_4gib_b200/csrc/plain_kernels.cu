@@ -632,11 +632,15 @@ extern "C" int llm_attention_plain(const void* q, void* out, int dtype, void* k_
 
 // ------------------------------------------------------------------------------- SwiGLU
 
-// out[t, i] = silu(gate[t, i]) * up[t, i] with gate = in[t, i] and up = in[t, inter + i]; `in`
-// may be a sum of partial results.
+// out[t, i] = act(gate[t, i]) * up[t, i] with gate = in[t, i] and up = in[t, inter + i]; `in`
+// may be a sum of partial results.  act: silu (GLU_SILU), or the tanh form of gelu,
+// 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))) (GLU_GELU_TANH).
+#define GLU_SILU 0
+#define GLU_GELU_TANH 1
+
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ in, int n_partials, long long partial_stride,
-                              TO* __restrict__ out, long long total, int inter) {
+                              TO* __restrict__ out, long long total, int inter, int act) {
   pdl_launch_dependents();
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -648,18 +652,36 @@ __global__ void swiglu_kernel(const TI* __restrict__ in, int n_partials, long lo
       g += to_float(in[p * partial_stride + t * 2 * inter + c]);
       u += to_float(in[p * partial_stride + t * 2 * inter + inter + c]);
     }
-    out[i] = from_float<TO>(g / (1.0f + expf(-g)) * u);
+    const float a = act == GLU_GELU_TANH
+                        ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
+                        : g / (1.0f + expf(-g));
+    out[i] = from_float<TO>(a * u);
   }
 }
 
+static int glu_launch(const void* in, int in_dtype, int n_partials, long long partial_stride, void* out,
+                      int out_dtype, int n_tokens, int inter, int act, cudaStream_t stream);
+
 extern "C" int llm_swiglu(const void* in, int in_dtype, int n_partials, long long partial_stride,
                           void* out, int out_dtype, int n_tokens, int inter, cudaStream_t stream) {
+  return glu_launch(in, in_dtype, n_partials, partial_stride, out, out_dtype, n_tokens, inter, GLU_SILU, stream);
+}
+
+// The same with the activation named by `act`.
+extern "C" int llm_glu(const void* in, int in_dtype, int n_partials, long long partial_stride, void* out,
+                       int out_dtype, int n_tokens, int inter, int act, cudaStream_t stream) {
+  LLM_HOST_CHECK(act == GLU_SILU || act == GLU_GELU_TANH, ERR_BAD_SIZE);
+  return glu_launch(in, in_dtype, n_partials, partial_stride, out, out_dtype, n_tokens, inter, act, stream);
+}
+
+static int glu_launch(const void* in, int in_dtype, int n_partials, long long partial_stride, void* out,
+                      int out_dtype, int n_tokens, int inter, int act, cudaStream_t stream) {
   const long long total = (long long)n_tokens * inter;
   if (total <= 0) return 0;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
 #define LAUNCH_SWIGLU(TI, TO)                                                                    \
   launch_kernel(swiglu_kernel<TI, TO>, blocks, 256, 0, stream, (const TI*)in, n_partials,        \
-                partial_stride, (TO*)out, total, inter)
+                partial_stride, (TO*)out, total, inter, act)
   if (in_dtype == DT_F32 && out_dtype == DT_F32) LAUNCH_SWIGLU(float, float);
   else if (in_dtype == DT_F32 && out_dtype == DT_BF16) LAUNCH_SWIGLU(float, __nv_bfloat16);
   else if (in_dtype == DT_BF16 && out_dtype == DT_BF16) LAUNCH_SWIGLU(__nv_bfloat16, __nv_bfloat16);

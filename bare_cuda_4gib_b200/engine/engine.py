@@ -87,7 +87,7 @@ class LLMEngine:
             self.model = random_model(random[0], int(random[1]), dtype, device)
         else:
             self.model, self.config = load_model(model_path, dtype, device)
-        if max_tokens > self.model.spec.max_positions:
+        if self.model.spec.max_positions is not None and max_tokens > self.model.spec.max_positions:
             raise EngineError(f"max_tokens {max_tokens} exceeds the model's {self.model.spec.max_positions} positions")
         if max_seqs <= 0:
             raise EngineError("max_seqs must be positive")

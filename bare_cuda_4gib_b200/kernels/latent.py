@@ -1,0 +1,69 @@
+"""Launchers of `csrc/latent_attention.cu`: attention over a cached latent vector per token."""
+
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+from .lib import CacheView, _check, _dev, _ptr, dtype_code
+
+MAX_RANK = 512      # value entries the attention kernel keeps per lane times 32
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        l = build.load_library("latent_attention.cu")
+        P, I, L, F = c_void_p, c_int, c_longlong, c_float
+        l.llm_latent_prepare.argtypes = [P, I, L, I, I, I, I, I, I, P, F, P, I, F, P, P, P, L, I, I, P, P, I, I, P]
+        l.llm_per_head_linear.argtypes = [P, L, L, P, I, P, L, L, P, L, I, I, I, I, I, P]
+        l.llm_latent_attention.argtypes = [P, P, I, P, P, L, I, I, I, I, P, P, P, I, I, F, I, P]
+        for name in ("llm_latent_prepare", "llm_per_head_linear", "llm_latent_attention"):
+            getattr(l, name).restype = c_int
+        _lib = l
+    return _lib
+
+
+def prepare(ctx, u: torch.Tensor, q_col: int, c_col: int, heads: int, dim: int, rot: int, rank: int,
+            norm_w: torch.Tensor, eps: float, inv_freq: Optional[torch.Tensor], rot_dims: int, mag: float,
+            q_full: torch.Tensor, cache: CacheView, write_cache: bool) -> None:
+    """Norms the latent, rotates the shared key part and writes both to the cache; rotates the
+    queries' rotated parts into the last `rot` entries of q_full [rows, heads, rank + rot]."""
+    _dev(u, norm_w, inv_freq, q_full)
+    _check(lib().llm_latent_prepare(
+        u.data_ptr(), dtype_code(u.dtype), u.stride(0), q_col, c_col, heads, dim, rot, rank, norm_w.data_ptr(),
+        float(eps), _ptr(inv_freq), int(rot_dims), float(mag), q_full.data_ptr(), cache.k_ptr,
+        cache.block_table.data_ptr(), cache.page_stride, cache.table_stride, cache.page_tokens,
+        ctx.positions.data_ptr(), ctx.row_seq.data_ptr(), 1 if write_cache else 0, ctx.n_tokens, ctx.stream),
+        "latent_prepare")
+
+
+def per_head_linear(ctx, x: torch.Tensor, w: torch.Tensor, w_in_rows: bool, out: torch.Tensor, heads: int, n_in: int,
+                    n_out: int, rows: int, gate: Optional[torch.Tensor] = None) -> None:
+    """out[t, h, :n_out] = x[t, h, :n_in] times head h's block of w: rows h * n_in .. of
+    w [heads * n_in, n_out] (`w_in_rows`), or the transpose of rows h * n_out .. of w [heads * n_out,
+    n_in].  x and out are [rows, heads, >= n] views (any row and head strides); with `gate`
+    [rows, heads * n_out] the result is multiplied by its sigmoid."""
+    _dev(x, w, out, gate)
+    if not (x.dtype == w.dtype == out.dtype) or x.stride(2) != 1 or out.stride(2) != 1 or not w.is_contiguous():
+        raise TypeError("per_head_linear: element types or layout not as the kernel needs")
+    _check(lib().llm_per_head_linear(
+        x.data_ptr(), x.stride(0), x.stride(1), w.data_ptr(), 1 if w_in_rows else 0, out.data_ptr(), out.stride(0),
+        out.stride(1), _ptr(gate), gate.stride(0) if gate is not None else 0, dtype_code(x.dtype), rows, heads, n_in,
+        n_out, ctx.stream), "per_head_linear")
+
+
+def attention(ctx, q_full: torch.Tensor, out: torch.Tensor, cache: CacheView, rank: int, sink: Optional[torch.Tensor],
+              heads: int, scale: float, window: int = 0) -> None:
+    """out[t, h] = sum_j p_j c_j over the cached vectors [c_j | r_j] at positions <= the query's, p the
+    softmax of (q_full[t, h] . [c_j | r_j]) * scale, with exp(sink[h]) in the denominator if given."""
+    _dev(q_full, out, sink)
+    _check(lib().llm_latent_attention(
+        q_full.data_ptr(), out.data_ptr(), dtype_code(q_full.dtype), cache.k_ptr, cache.block_table.data_ptr(),
+        cache.page_stride, cache.table_stride, cache.page_tokens, cache.head_dim, rank, _ptr(sink),
+        ctx.positions.data_ptr(), ctx.row_seq.data_ptr(), heads, ctx.n_tokens, float(scale), int(window), ctx.stream),
+        "latent_attention")

@@ -6,7 +6,8 @@ ATTENTION_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128)
 
 def all_libraries():
     jobs = [("plain_kernels.cu", ()), ("gemm_tcgen05.cu", ()), ("gemv_fused.cu", ()), ("stream_kernels.cu", ()),
-            ("linear_attention.cu", ()), ("biased_attention.cu", ())]
+            ("linear_attention.cu", ()), ("biased_attention.cu", ()), ("sandwich_norm.cu", ()), ("head_prepare.cu", ()),
+            ("latent_attention.cu", ()), ("mlstm.cu", ())]
     jobs += [("attention_mma.cu", (f"-DHEAD_DIM={d}",)) for d in ATTENTION_HEAD_DIMS]
     jobs += [("attention_mma.cu", (f"-DHEAD_DIM={d}", "-DDISTANCE_BIAS")) for d in ATTENTION_HEAD_DIMS]
     jobs += [("attention_tcgen05.cu", (f"-DHEAD_DIM={d}",)) for d in (64, 128)]

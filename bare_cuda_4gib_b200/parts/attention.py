@@ -107,3 +107,99 @@ class Attention(Part):
         residual = getattr(ctx, "residual", None)
         return self.o.forward(ctx, out, n, torch.float32, "attn_proj", allow_partials=True,
                               epilogue=K.AddTo(residual, getattr(ctx, "following_norm", None)) if residual is not None else None)
+
+
+@register_mixer("gated_attention")
+class GatedAttention(Part):
+    """Grouped-query softmax attention whose queries and keys are RMS-normed per head (one weight
+    per projection, shared by its heads) before the position encoding turns them, whose scores are
+    (q . k) * `scale`, and whose concatenated heads are multiplied by sigmoid(Wg h) before the output
+    projection.  With `values` = "keys" there is no value projection: a token's value is its key as
+    projected, before norm and rotation.  `window` (None = every key) keeps the last positions.
+
+    One product makes [q | k (| v) | g]; one kernel norms, turns and caches; then the engine's paged
+    attention kernels run as they do for "attention".
+
+    params: `hidden`, `heads`, `kv_heads`, `head_dim`, `window`, `scale`, `eps`, `values`
+    ("keys" | "projection"), `position` (a `PartSpec`; "rotary_pairs" or "none").
+    tensors: `q`, `k`, (`v`,) `g`, `o`, `q_norm` [head_dim], `k_norm` [head_dim]."""
+
+    takes_lazy_input = False
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden, self.heads, self.kv_heads, self.head_dim = (
+            int(p["hidden"]), int(p["heads"]), int(p["kv_heads"]), int(p["head_dim"]))
+        self.window = p.get("window")
+        self.own_values = p.get("values", "projection") != "keys"
+        if self.heads % self.kv_heads:
+            raise ConfigError(f"gated_attention: {self.heads} heads cannot share {self.kv_heads} key/value heads")
+        self.position = build_part("position", p["position"])
+        self.scale = float(p.get("scale") or 1.0 / math.sqrt(self.head_dim))
+        self.eps = float(p["eps"])
+
+    def children(self):
+        return [self.position]
+
+    def _projections(self):
+        return ("q", "k", "v", "g") if self.own_values else ("q", "k", "g")
+
+    def local_weights(self):
+        qd, kvd = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        out = {"q": ((qd, self.hidden), "matrix"), "k": ((kvd, self.hidden), "matrix"),
+               "g": ((qd, self.hidden), "matrix"), "o": ((self.hidden, qd), "matrix"),
+               "q_norm": ((self.head_dim,), "norm"), "k_norm": ((self.head_dim,), "norm")}
+        if self.own_values:
+            out["v"] = ((kvd, self.hidden), "matrix")
+        return out
+
+    def adjacent_weights(self):
+        return [self._projections()]
+
+    def cache_request(self):
+        return KVCacheRequest(self.kv_heads, self.head_dim, self.window)
+
+    def state_request(self):
+        return None
+
+    def prepare(self, dtype, device) -> None:
+        t = self.tensors
+        self.proj = Linear(fused_rows([t[n] for n in self._projections()]), "gated_attention.in")
+        self.o = Linear(t["o"], "gated_attention.o")
+        self.proj.prepare(dtype)
+        self.o.prepare(dtype)
+        self.q_norm, self.k_norm = t["q_norm"].to(dtype).contiguous(), t["k_norm"].to(dtype).contiguous()
+        self.position.prepare(dtype, device)
+        self.inv_freq = getattr(self.position, "inv_freq", None)
+        self.rot_dims = int(getattr(self.position, "dims", 0)) if self.inv_freq is not None else 0
+        if self.rot_dims > self.head_dim:
+            raise ConfigError(f"gated_attention: {self.rot_dims} rotated entries in a head of {self.head_dim}")
+        self.magnitude = float(getattr(self.position, "magnitude", 1.0))
+        self.fast = None
+        if dtype == torch.bfloat16 and device.type == "cuda":
+            from ..kernels import attention as fast
+            self.fast = fast.plan_for(self.head_dim, self.heads, self.kv_heads)
+
+    def plan_step(self, ctx) -> None:
+        if self.fast is not None and ctx.use_fast_attention:
+            from ..kernels import attention as fast
+            fast.step_tiles(ctx, self.fast)
+
+    def forward(self, ctx, call, h):
+        from ..kernels import head_prepare as HP
+        n = ctx.n_tokens
+        qd, kvd = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        u = self.proj.forward(ctx, h, n, ctx.dtype, "mixer_in").tensor
+        q = ctx.ws.get("q", (n, qd), ctx.dtype)
+        HP.headnorm_rope_cache(ctx, u, 0, qd, qd + kvd if self.own_values else -1, self.q_norm, self.k_norm, self.eps,
+                               self.inv_freq, self.rot_dims, self.magnitude, q, call.cache, self.heads, call.writes_cache)
+        out = ctx.ws.get("attn_out", (n, qd), ctx.dtype)
+        window = int(self.window) if self.window else 0
+        if self.fast is not None and ctx.use_fast_attention:
+            from ..kernels import attention as fast
+            fast.run(ctx, self.fast, q, out, call.cache, self.scale, window)
+        else:
+            K.attention_plain(q, out, call.cache, ctx.positions, ctx.row_seq, self.heads, n, self.scale, window, ctx.stream)
+        HP.sigmoid_gate(ctx, out, u[:, u.shape[1] - qd:], n)
+        return self.o.forward(ctx, out, n, torch.float32, "attn_proj", allow_partials=True)

@@ -43,3 +43,44 @@ class PreNormBlock:
     def entry_norm(self):
         """The norm that reads the residual stream first when this layer runs."""
         return self.mixer_norm
+
+
+@register_block("sandwich")
+class SandwichBlock:
+    """x += norm_b(mixer(norm(x))), then (if the layer has a feed-forward) the same around it.  The
+    norms behind the sublayers are `layer_spec.extras["post1"]` and `["post2"]`.  A sublayer's result is
+    handed on un-normed and un-added; the norm that reads the stream next does both first."""
+
+    def __init__(self, layer_spec):
+        self.mixer_norm = build_part("norm", layer_spec.mixer_norm)
+        self.mixer = build_part("mixer", layer_spec.mixer)
+        self.post1 = build_part("norm", layer_spec.extras["post1"])
+        self.has_ffn = layer_spec.ffn is not None
+        if self.has_ffn:
+            self.ffn_norm = build_part("norm", layer_spec.ffn_norm)
+            self.ffn = build_part("feed_forward", layer_spec.ffn)
+            self.post2 = build_part("norm", layer_spec.extras["post2"])
+
+    def parts(self):
+        out = [self.mixer_norm, self.mixer, self.post1]
+        if self.has_ffn:
+            out += [self.ffn_norm, self.ffn, self.post2]
+        return out
+
+    def cache_demands(self):
+        many = getattr(self.mixer, "cache_demands", None)
+        return many() if many else [(self.mixer.cache_request(), self.mixer.state_request())]
+
+    def entry_norm(self):
+        return self.mixer_norm
+
+    def forward(self, ctx, call, residual, pending):
+        n = ctx.n_tokens
+        ctx.residual = None          # sublayers hand their result back: it is normed before it is added
+        ctx.following_norm = None
+        h = self.mixer_norm.forward(ctx, residual, pending, n)
+        pending = self.post1.pending(self.mixer.forward(ctx, call, h))
+        if self.has_ffn:
+            h = self.ffn_norm.forward(ctx, residual, pending, n)
+            pending = self.post2.pending(self.ffn.forward(ctx, h))
+        return pending

@@ -69,3 +69,24 @@ class ScaledPositionEmbedding(Part):
         SK.embed_positions(self.tensors["weight"], self.tensors.get("positions"), ctx.token_ids, ctx.positions, x,
                            ctx.n_tokens, width, streams, float(p.get("scale", 1.0)), ctx.stream)
         return x
+
+
+@register_embedding("table_norm")
+class NormedEmbedding(Part):
+    """x = rms_norm(E[id]) * w, in float32.
+
+    params: `vocab`, `hidden`, `eps`.  tensors: `weight` [vocab, hidden], `norm` [hidden]."""
+
+    def local_weights(self):
+        p = self.params
+        return {"weight": ((int(p["vocab"]), int(p["hidden"])), "matrix"), "norm": ((int(p["hidden"]),), "norm")}
+
+    def prepare(self, dtype, device) -> None:
+        self.norm = self.tensors["norm"].to(self.tensors["weight"].dtype).contiguous()
+
+    def forward(self, ctx) -> torch.Tensor:
+        from ..kernels import sandwich as SW
+        x = ctx.ws.get("residual", (ctx.n_tokens, int(self.params["hidden"])), torch.float32)
+        SW.embed_rmsnorm(self.tensors["weight"], ctx.token_ids, self.norm, x, ctx.n_tokens, float(self.params["eps"]),
+                         ctx.stream)
+        return x

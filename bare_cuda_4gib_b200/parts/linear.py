@@ -32,12 +32,17 @@ class Linear:
             self.few = gemv.supports(self.weight)
 
     def forward(self, ctx, a, rows: int, out_dtype: torch.dtype, buffer: str,
-                allow_partials: bool = False, swiglu: bool = False, epilogue=None) -> Optional[K.Partials]:
+                allow_partials: bool = False, swiglu: bool = False, epilogue=None,
+                glu: Optional[str] = None) -> Optional[K.Partials]:
         """a[:rows] @ W^T into the workspace buffer `buffer`.  With `swiglu`, W is [gate; up] and
         the result is silu(gate) * up of half the width (fused where the kernel can).  `a` is a
         matrix or a `LazyNorm`.  `epilogue` (`AddTo`, `RotateAndCache`) names what the caller will
         do with the result next: a kernel that can do it itself does, and None comes back; from
-        every other kernel the plain result comes back and the epilogue stays the caller's."""
+        every other kernel the plain result comes back and the epilogue stays the caller's.
+        `glu` names the activation of a gated product ("silu" is what `swiglu` asks for)."""
+        if glu is not None and glu != "silu":
+            return self._glu(ctx, a, rows, out_dtype, buffer, glu)
+        swiglu = swiglu or glu == "silu"
         width = self.out_features // 2 if swiglu else self.out_features
         if self.few and ctx.use_fast_gemm:
             from ..kernels import gemv
@@ -55,4 +60,13 @@ class Linear:
             return K.Partials(out)
         out = ctx.ws.get(buffer, (rows, width), out_dtype)
         K.matmul_plain(a, self.weight, out, rows, ctx.stream)
+        return K.Partials(out)
+
+    def _glu(self, ctx, a, rows: int, out_dtype: torch.dtype, buffer: str, activation: str) -> K.Partials:
+        """W = [gate; up]: activation(gate) * up, the product first and the activation as a kernel of
+        its own over its (partial) sums."""
+        full = self.forward(ctx, a, rows, torch.float32 if rows <= 256 else out_dtype, buffer + ".gate_up",
+                            allow_partials=True)
+        out = ctx.ws.get(buffer, (rows, self.out_features // 2), out_dtype)
+        K.glu(full, out, rows, activation, ctx.stream)
         return K.Partials(out)

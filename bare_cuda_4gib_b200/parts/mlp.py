@@ -73,3 +73,36 @@ class DenseFeedForward(Part):
         act = ctx.ws.get("ffn_act", (n, int(self.params["intermediate"])), ctx.dtype)
         SK.activation(z, act, n, self.params.get("activation", "relu2"), ctx.stream)
         return self.down.forward(ctx, act, n, torch.float32, "ffn_out", allow_partials=True)
+
+
+@register_feed_forward("glu")
+class GatedFeedForward(Part):
+    """down(act(gate(h)) * up(h)), no biases; `activation` is "silu" or "gelu_tanh" (the tanh form of
+    gelu).  gate and up are one matrix product against [Wgate; Wup]; the kernels that fuse the
+    activation into that product do so for both activations.
+
+    params: `hidden`, `intermediate`, `activation`.  tensors: `gate`, `up`, `down`."""
+
+    takes_lazy_input = False
+
+    def local_weights(self):
+        h, i = int(self.params["hidden"]), int(self.params["intermediate"])
+        return {"gate": ((i, h), "matrix"), "up": ((i, h), "matrix"), "down": ((h, i), "matrix")}
+
+    def adjacent_weights(self):
+        return [("gate", "up")]
+
+    def prepare(self, dtype, device) -> None:
+        self.activation = self.params.get("activation", "silu")
+        if self.activation not in K.GLU_ACTIVATIONS:
+            raise KeyError(f"glu feed-forward: activation '{self.activation}' is not one of {sorted(K.GLU_ACTIVATIONS)}")
+        t = self.tensors
+        self.gate_up = Linear(fused_rows([t.pop("gate"), t.pop("up")]), "gate_up")
+        self.down = Linear(t.pop("down"), "down")
+        self.gate_up.prepare(dtype)
+        self.down.prepare(dtype)
+
+    def forward(self, ctx, h):
+        n = ctx.n_tokens
+        act = self.gate_up.forward(ctx, h, n, ctx.dtype, "ffn_act", glu=self.activation)
+        return self.down.forward(ctx, act.tensor, n, torch.float32, "ffn_out", allow_partials=True)

@@ -44,3 +44,30 @@ class RMSNorm(Part):
         K.add_rmsnorm(residual, delta, self.tensors["weight"], out, float(self.params["eps"]), rows,
                       row_index, ctx.stream)
         return out
+
+
+@register_norm("sandwich_rmsnorm")
+class SandwichRMSNorm(Part):
+    """RMS norm of a stream whose sublayers are normed on both sides, x <- x + norm_b(f(norm(x))).
+    As the norm before a sublayer it first adds what is pending, a `NormedDelta` (the previous
+    sublayer's result with the weight of its norm behind), in the same kernel; as the norm behind a
+    sublayer it only lends its weight (`pending`).
+
+    params: `size`, `eps`.  tensors: `weight` [size]."""
+
+    def local_weights(self):
+        return {"weight": ((self.params["size"],), "norm")}
+
+    def prepare(self, dtype, device) -> None:
+        self.weight = self.tensors["weight"].to(dtype).contiguous()
+
+    def pending(self, y):
+        from ..kernels.sandwich import NormedDelta
+        return NormedDelta(y, self.weight, float(self.params["eps"]))
+
+    def forward(self, ctx, residual: torch.Tensor, delta, rows: int, row_index: Optional[torch.Tensor] = None,
+                buffer: str = "normed", lazy: bool = False):
+        from ..kernels import sandwich as SW
+        out = ctx.ws.get(buffer, (rows, self.params["size"]), ctx.dtype)
+        SW.postnorm_add_rmsnorm(residual, delta, self.weight, out, float(self.params["eps"]), rows, row_index, ctx.stream)
+        return out

@@ -35,3 +35,44 @@ class NoPositions(Part):
 
     def fused_rotation(self):
         return None
+
+
+@register_position("rotary_pairs")
+class PairwiseRotaryPositions(Part):
+    """Rotation of the first `dims` entries of a head in neighbouring pairs (entry 2i with 2i + 1;
+    the rest pass) by the angle position * f_i, f_i = base^(-2i / dims).
+
+    With `scaling` {factor, original, fast, slow} (YaRN): a frequency that turns more than `fast`
+    times within `original` positions keeps f_i, one that turns fewer than `slow` times becomes
+    f_i / factor, in between the two are blended linearly in i; cos and sin are multiplied by
+    0.1 ln(factor) + 1.  With where(t) = dims ln(original / (2 pi t)) / (2 ln base), lo =
+    max(floor(where(fast)), 0), hi = min(ceil(where(slow)), dims - 1), ramp_i = clamp((i - lo) /
+    max(hi - lo, 0.001), 0, 1): f_i <- f_i / factor * ramp_i + f_i (1 - ramp_i).
+
+    The kernels that norm and cache q and k turn them with `inv_freq` and `magnitude` themselves.
+    params: `dims`, `base`, `scaling` (or None).  No tensors."""
+
+    def prepare(self, dtype, device) -> None:
+        import math
+
+        dims, base = int(self.params["dims"]), float(self.params["base"])
+        self.dims = dims
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        f = base ** (-2.0 * i / dims)
+        self.magnitude = 1.0
+        sc = self.params.get("scaling")
+        if sc:
+            factor, original = float(sc["factor"]), float(sc["original"])
+
+            def where(turns: float) -> float:
+                return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+            lo = max(math.floor(where(float(sc["fast"]))), 0)
+            hi = min(math.ceil(where(float(sc["slow"]))), dims - 1)
+            ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            f = f / factor * ramp + f * (1.0 - ramp)
+            self.magnitude = 0.1 * math.log(factor) + 1.0
+        self.inv_freq = f.to(torch.float32).to(device)
+
+    def fused_rotation(self):
+        return None      # the pairing differs from the one the fused attention kernels apply

@@ -62,7 +62,7 @@ class ModelSpec:
     architecture: str
     hidden_size: int
     vocab_size: int
-    max_positions: int
+    max_positions: Optional[int]      # None: the design states no largest position
     embed: PartSpec
     layers: List[LayerSpec]
     order: List[LayerCall]

@@ -108,9 +108,8 @@ class ZaduraxConfig:
                 other = self.layers[src]
                 if isinstance(other, dict) and other.get("weights_of") is not None:
                     raise ConfigError(f"config.json: '{where}weights_of' names layer {src}, which has no tensors of its own")
-                same = isinstance(other, dict) and all(other.get(k) == layer.get(k) for k in ("type", "mixer", "mlp"))
-                if not same:
-                    raise ConfigError(f"config.json: '{where}' uses the tensors of layer {src} but differs from it")
+                if not isinstance(other, dict) or other.get("type") != layer["type"]:
+                    raise ConfigError(f"config.json: '{where}type' differs from layer {src}, whose tensors it uses")
 
     def to_dict(self) -> Dict[str, Any]:
         """The config.json this configuration is read back from."""

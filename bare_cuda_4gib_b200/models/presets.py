@@ -48,6 +48,34 @@ PRESETS.update({
 })
 
 
+def _zadurax(width, vocab, ff, heads, head_dim, kv_heads, window, latent_heads, latent_dim, rot_dim, kv_rank,
+             state_heads, state_dim, repeats):
+    """One layer of each mixer with a feed-forward, then `repeats` more runs of the three with the same tensors."""
+    own = [{"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff},
+            "mixer": {"heads": latent_heads, "dim": latent_dim, "rot_dim": rot_dim, "vdim": latent_dim, "kv_rank": kv_rank,
+                      "scale": (latent_dim + rot_dim) ** -0.5,
+                      "rot": {"base": 10000.0, "dims": rot_dim,
+                              "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}},
+           {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+            "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "mask": {"size": window},
+                      "rot": {"base": 10000.0, "dims": head_dim // 2}, "scale": head_dim ** -0.5}},
+           {"type": "mlstm", "mlp": {"kind": "dense", "ff": ff},
+            "mixer": {"heads": state_heads, "dim": state_dim, "vdim": state_dim, "gate_cap": 15.0}}]
+    layers = list(own)
+    for _ in range(repeats):
+        layers += [dict(layer, weights_of=j) for j, layer in enumerate(own)]
+    return dict(architecture="Zadurax", vocab=vocab, width=width, norm={"eps": 1e-6}, layers=layers)
+
+
+PRESETS.update({
+    "zadurax-tiny": _zadurax(64, 300, 96, 4, 16, 2, 24, 2, 16, 8, 24, 2, 16, 1),
+    # layer sizes near TinyLlama's (width 2048, feed-forward 5632)
+    "zadurax-2048": _zadurax(2048, 32000, 5632, 32, 64, 4, 1024, 16, 64, 32, 256, 16, 128, 1),
+    # ... and near Llama-2-7B's (width 4096, feed-forward 11008)
+    "zadurax-4096": _zadurax(4096, 32000, 11008, 32, 128, 8, 1024, 32, 128, 64, 512, 16, 256, 1),
+})
+
+
 def preset_config(name: str, **overrides):
     from ..config.llama import LlamaConfig
     from ..errors import ConfigError

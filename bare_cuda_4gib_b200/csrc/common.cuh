@@ -74,6 +74,16 @@ __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
   return __float2bfloat16_rn(v);
 }
 
+// The activation on the gate of a gated feed-forward, as the products fuse it: silu, or (a library
+// built with -DGLU_GELU_TANH) the tanh form of gelu, 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float glu_act(float z) {
+#ifdef GLU_GELU_TANH
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+#else
+  return z / (1.0f + expf(-z));
+#endif
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -302,3 +302,342 @@ extern "C" int llm_latent_attention(const void* q, void* out, int dtype, void* k
   }
   return launch_status();
 }
+
+// ------------------------------------------------------------------------------ attention, tensor cores
+
+// The same attention on mma.sync (bfloat16 operands, float32 sums) for bfloat16 steps whose sizes
+// fit: D a multiple of 16, rank a multiple of 32 up to 512.  Grid (token x group of 16 heads, key
+// split).  All 16 rows of a tile are one token's heads: they see the same keys, so a tile has one
+// causal limit and one cached block serves all of them, as the K operand [keys][D] of S = Q K^T and,
+// its first `rank` columns, as the V operand of O += P V, from the same shared memory.  Four warps:
+// for S a warp takes a quarter of the block's keys (all D), for O a quarter of the value columns
+// (all keys); P and the rows' maxima and sums cross between the warps through shared memory.  The
+// running maximum and sum are kept (identically) by every warp; weights are base-2 exponentials of
+// scores scaled by scale * log2(e).  Key blocks are KB positions wide and start at multiples of KB;
+// the next block arrives by asynchronous copies while the current one is used.  With n_splits > 1 the
+// key blocks are dealt to blockIdx.y in runs, every block writes (O, max, sum) unnormalised, and the
+// merge kernel adds them up with the sink; else the block finishes its rows itself.
+#define LM_THREADS 128
+#define LM_MAX_NT 16
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t (&r)[2], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// 16 bytes from global to shared memory, or 16 zero bytes
+__device__ __forceinline__ void cp_async_16_or_zero(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src),
+               "r"(bytes) : "memory");
+}
+
+template <int KB>
+__global__ void __launch_bounds__(LM_THREADS)
+latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                            float* __restrict__ partial, PagedCache cache, int rank,
+                            const __nv_bfloat16* __restrict__ sink, const int32_t* __restrict__ positions,
+                            const int32_t* __restrict__ row_seq, int heads, int head_groups, float scale_log2,
+                            int window, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) uint8_t lm_smem[];
+  constexpr int NT_S = KB / 32, PLD = KB + 8;
+  const int D = cache.head_dim, ld = D + 8, chunks = D / 8;
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(lm_smem);      // [16][ld]
+  __nv_bfloat16* ks = qs + 16 * ld;                                   // [2][KB][ld]
+  __nv_bfloat16* ps = ks + 2 * KB * ld;                               // [16][PLD]
+  float* red = reinterpret_cast<float*>(ps + 16 * PLD);               // [2][4][16]: maxima, sums
+  long long* koff = reinterpret_cast<long long*>(red + 128);          // [2][KB]: a key's place in the pool, -1: none
+  const int tile = blockIdx.x, t = tile / head_groups, hg = tile - t * head_groups, split = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos = positions[t], seq = row_seq[t];
+  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  const int b_lo = first / KB, nb = pos / KB - b_lo + 1;
+  const int per = (nb + n_splits - 1) / n_splits;
+  const int b0 = b_lo + split * per, b1 = min(b_lo + nb, b0 + per);
+  const __nv_bfloat16* kc = (const __nv_bfloat16*)cache.k;
+
+  for (int idx = threadIdx.x; idx < 16 * chunks; idx += LM_THREADS) {
+    const int r = idx / chunks, c = idx - r * chunks, h = hg * 16 + r;
+    const bool valid = h < heads;
+    cp_async_16_or_zero(qs + r * ld + c * 8, q + ((long long)t * heads + (valid ? h : 0)) * D + c * 8, valid);
+  }
+  auto offsets = [&](int b, int stage) {
+    if (threadIdx.x < KB) {
+      const int j = b * KB + threadIdx.x;
+      long long off = -1;
+      if (j >= first && j <= pos) {
+        const int page = cache.block_table[(long long)seq * cache.table_stride + j / cache.page_tokens];
+        if (page >= 0) off = (long long)page * cache.page_stride + (long long)(j % cache.page_tokens) * D;
+      }
+      koff[stage * KB + threadIdx.x] = off;
+    }
+  };
+  auto copies = [&](int stage) {
+    __nv_bfloat16* dst = ks + stage * KB * ld;
+    for (int idx = threadIdx.x; idx < KB * chunks; idx += LM_THREADS) {
+      const int kk = idx / chunks, c = idx - kk * chunks;
+      const long long off = koff[stage * KB + kk];
+      cp_async_16_or_zero(dst + kk * ld + c * 8, kc + (off >= 0 ? off : 0) + c * 8, off >= 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (b0 < b1) {
+    offsets(b0, 0);
+    __syncthreads();
+    copies(0);
+  } else {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+
+  const int r0 = lane >> 2;                 // this thread's rows: r0 and r0 + 8
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+  float o[LM_MAX_NT][4];
+#pragma unroll
+  for (int i = 0; i < LM_MAX_NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  const int ntw = rank / 32, col0 = warp * (rank / 4);
+
+  for (int b = b0; b < b1; ++b) {
+    const int stage = (b - b0) & 1;
+    if (b + 1 < b1) offsets(b + 1, stage ^ 1);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                         // block b (and q) have arrived; the other stage is free; offsets are seen
+    if (b + 1 < b1) copies(stage ^ 1);
+    // S = Q K^T for this warp's keys
+    float s[NT_S][4];
+#pragma unroll
+    for (int i = 0; i < NT_S; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+    const __nv_bfloat16* kb = ks + (stage * KB + warp * (KB / 4)) * ld;
+    for (int k0 = 0; k0 < D; k0 += 16) {
+      uint32_t a[4];
+      ldsm_x4(a, qs + (lane & 15) * ld + k0 + (lane >> 4) * 8);
+      if constexpr (NT_S == 2) {
+        uint32_t bb[4];
+        ldsm_x4(bb, kb + ((lane & 7) + ((lane >> 4) & 1) * 8) * ld + k0 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[0], a, bb[0], bb[1]);
+        mma_bf16(s[1], a, bb[2], bb[3]);
+      } else {
+        uint32_t bb[2];
+        ldsm_x2(bb, kb + (lane & 7) * ld + k0 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[0], a, bb[0], bb[1]);
+      }
+    }
+    // scale, mask, the rows' maxima over this warp's keys
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NT_S; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = warp * (KB / 4) + i * 8 + (lane & 3) * 2 + (e & 1);
+        const float v = koff[stage * KB + key] >= 0 ? s[i][e] * scale_log2 : -INFINITY;
+        s[i][e] = v;
+        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+      }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    if ((lane & 3) == 0) {
+      red[warp * 16 + r0] = mx0;
+      red[warp * 16 + r0 + 8] = mx1;
+    }
+    __syncthreads();
+    float n0 = m0, n1 = m1;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      n0 = fmaxf(n0, red[w * 16 + r0]);
+      n1 = fmaxf(n1, red[w * 16 + r0 + 8]);
+    }
+    const float c0 = n0 == -INFINITY ? 1.0f : exp2f(m0 - n0), c1 = n1 == -INFINITY ? 1.0f : exp2f(m1 - n1);
+    float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NT_S; ++i) {
+      const float p0 = n0 == -INFINITY ? 0.0f : exp2f(s[i][0] - n0), p1 = n0 == -INFINITY ? 0.0f : exp2f(s[i][1] - n0);
+      const float p2 = n1 == -INFINITY ? 0.0f : exp2f(s[i][2] - n1), p3 = n1 == -INFINITY ? 0.0f : exp2f(s[i][3] - n1);
+      sum0 += p0 + p1;
+      sum1 += p2 + p3;
+      const int key = warp * (KB / 4) + i * 8 + (lane & 3) * 2;
+      *reinterpret_cast<__nv_bfloat162*>(ps + r0 * PLD + key) = __floats2bfloat162_rn(p0, p1);
+      *reinterpret_cast<__nv_bfloat162*>(ps + (r0 + 8) * PLD + key) = __floats2bfloat162_rn(p2, p3);
+    }
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+    if ((lane & 3) == 0) {
+      red[64 + warp * 16 + r0] = sum0;
+      red[64 + warp * 16 + r0 + 8] = sum1;
+    }
+    __syncthreads();
+    l0 = l0 * c0 + red[64 + r0] + red[64 + 16 + r0] + red[64 + 32 + r0] + red[64 + 48 + r0];
+    l1 = l1 * c1 + red[64 + r0 + 8] + red[64 + 16 + r0 + 8] + red[64 + 32 + r0 + 8] + red[64 + 48 + r0 + 8];
+    m0 = n0;
+    m1 = n1;
+    // O = O * corr + P V for this warp's value columns
+#pragma unroll
+    for (int i = 0; i < LM_MAX_NT; ++i)
+      if (i < ntw) {
+        o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
+      }
+    const __nv_bfloat16* vb = ks + stage * KB * ld + col0;
+#pragma unroll
+    for (int kk = 0; kk < KB; kk += 16) {
+      uint32_t a[4];
+      ldsm_x4(a, ps + (lane & 15) * PLD + kk + (lane >> 4) * 8);
+      const __nv_bfloat16* vrow = vb + (kk + (lane & 7) + ((lane >> 3) & 1) * 8) * ld;
+#pragma unroll
+      for (int i = 0; i < LM_MAX_NT; i += 2) {
+        if (i + 1 < ntw) {
+          uint32_t bb[4];
+          ldsm_x4_trans(bb, vrow + i * 8 + ((lane >> 4) & 1) * 8);
+          mma_bf16(o[i], a, bb[0], bb[1]);
+          mma_bf16(o[i + 1], a, bb[2], bb[3]);
+        } else if (i < ntw) {
+          uint32_t bb[2];
+          ldsm_x2_trans(bb, vrow + i * 8);
+          mma_bf16(o[i], a, bb[0], bb[1]);
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+  const int cq = (lane & 3) * 2;
+  if (n_splits > 1) {
+    float* dst = partial + ((long long)(tile * n_splits + split) * 16) * (rank + 2);
+#pragma unroll
+    for (int i = 0; i < LM_MAX_NT; ++i)
+      if (i < ntw) {
+        const int c = col0 + i * 8 + cq;
+        *reinterpret_cast<float2*>(dst + (long long)r0 * (rank + 2) + c) = make_float2(o[i][0], o[i][1]);
+        *reinterpret_cast<float2*>(dst + (long long)(r0 + 8) * (rank + 2) + c) = make_float2(o[i][2], o[i][3]);
+      }
+    if (warp == 0 && (lane & 3) == 0) {
+      *reinterpret_cast<float2*>(dst + (long long)r0 * (rank + 2) + rank) = make_float2(m0, l0);
+      *reinterpret_cast<float2*>(dst + (long long)(r0 + 8) * (rank + 2) + rank) = make_float2(m1, l1);
+    }
+    return;
+  }
+  const int h0 = hg * 16 + r0, h1 = h0 + 8;
+  if (sink) {
+    if (h0 < heads) {
+      const float sk = __bfloat162float(sink[h0]) * 1.4426950408889634f, n = fmaxf(m0, sk);
+      const float c = m0 == -INFINITY ? 0.0f : exp2f(m0 - n);
+      l0 = l0 * c + exp2f(sk - n);
+#pragma unroll
+      for (int i = 0; i < LM_MAX_NT; ++i) { o[i][0] *= c; o[i][1] *= c; }
+    }
+    if (h1 < heads) {
+      const float sk = __bfloat162float(sink[h1]) * 1.4426950408889634f, n = fmaxf(m1, sk);
+      const float c = m1 == -INFINITY ? 0.0f : exp2f(m1 - n);
+      l1 = l1 * c + exp2f(sk - n);
+#pragma unroll
+      for (int i = 0; i < LM_MAX_NT; ++i) { o[i][2] *= c; o[i][3] *= c; }
+    }
+  }
+  const float i0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, i1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+#pragma unroll
+  for (int i = 0; i < LM_MAX_NT; ++i)
+    if (i < ntw) {
+      const int c = col0 + i * 8 + cq;
+      if (h0 < heads)
+        *reinterpret_cast<__nv_bfloat162*>(out + ((long long)t * heads + h0) * rank + c) =
+            __floats2bfloat162_rn(o[i][0] * i0, o[i][1] * i0);
+      if (h1 < heads)
+        *reinterpret_cast<__nv_bfloat162*>(out + ((long long)t * heads + h1) * rank + c) =
+            __floats2bfloat162_rn(o[i][2] * i1, o[i][3] * i1);
+    }
+}
+
+// One block per (tile, row): the splits' (O, max, sum) and the sink -> the row's weighted latent.
+__global__ void __launch_bounds__(128)
+latent_attention_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                              const __nv_bfloat16* __restrict__ sink, int heads, int head_groups, int rank,
+                              int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tile = blockIdx.x >> 4, r = blockIdx.x & 15;
+  const int t = tile / head_groups, h = (tile - t * head_groups) * 16 + r;
+  if (h >= heads) return;
+  const float* base = partial + ((long long)tile * n_splits * 16 + r) * (rank + 2);
+  const long long step = (long long)16 * (rank + 2);
+  float top = sink ? __bfloat162float(sink[h]) * 1.4426950408889634f : -INFINITY;
+  const float sk = top;
+  for (int s = 0; s < n_splits; ++s) top = fmaxf(top, base[s * step + rank]);
+  float total = sink ? exp2f(sk - top) : 0.0f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float m = base[s * step + rank];
+    if (m != -INFINITY) total += base[s * step + rank + 1] * exp2f(m - top);
+  }
+  const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    float acc = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float m = base[s * step + rank];
+      if (m != -INFINITY) acc += base[s * step + c] * exp2f(m - top);
+    }
+    out[((long long)t * heads + h) * rank + c] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+// Floats of scratch a launch with these splits needs.
+extern "C" long long llm_latent_attention_mma_scratch(int n_tokens, int heads, int rank, int n_splits) {
+  return n_splits > 1 ? (long long)n_tokens * ((heads + 15) / 16) * n_splits * 16 * (rank + 2) : 0;
+}
+
+extern "C" int llm_latent_attention_mma(const void* q, void* out, float* partial, void* k_base,
+                                        const int32_t* block_table, long long page_stride, int table_stride,
+                                        int page_tokens, int D, int rank, const void* sink, const int32_t* positions,
+                                        const int32_t* row_seq, int heads, int n_tokens, float scale, int window,
+                                        int n_splits, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  LLM_HOST_CHECK(D % 16 == 0 && rank % 32 == 0 && rank >= 32 && rank <= 32 * LM_MAX_NT && rank <= D, ERR_BAD_SIZE);
+  LLM_HOST_CHECK(n_splits >= 1 && n_splits <= 65535 && (n_splits == 1 || partial), ERR_BAD_SIZE);
+  LLM_HOST_CHECK(((uintptr_t)q % 16) == 0 && ((uintptr_t)k_base % 16) == 0 && page_stride % 8 == 0, ERR_BAD_ALIGN);
+  PagedCache c{k_base, k_base, block_table, page_stride, table_stride, page_tokens, 1, D};
+  const int head_groups = (heads + 15) / 16;
+  const int ld = D + 8;
+  auto bytes = [&](int kb) {
+    return (size_t)(16 + 2 * kb) * ld * 2 + (size_t)16 * (kb + 8) * 2 + 128 * sizeof(float) + (size_t)2 * kb * sizeof(long long);
+  };
+  const int kb = bytes(64) <= 56 * 1024 ? 64 : 32;
+  const size_t smem = bytes(kb);
+  LLM_HOST_CHECK(smem <= 200 * 1024, ERR_BAD_SIZE);
+  dim3 grid((unsigned)((long long)n_tokens * head_groups), n_splits);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  if (kb == 64) {
+    auto kernel = latent_attention_mma_kernel<64>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_kernel(kernel, grid, LM_THREADS, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, c, rank,
+                  (const __nv_bfloat16*)sink, positions, row_seq, heads, head_groups, scale_log2, window, n_splits);
+  } else {
+    auto kernel = latent_attention_mma_kernel<32>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_kernel(kernel, grid, LM_THREADS, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, c, rank,
+                  (const __nv_bfloat16*)sink, positions, row_seq, heads, head_groups, scale_log2, window, n_splits);
+  }
+  int status = launch_status();
+  if (status || n_splits == 1) return status;
+  launch_kernel(latent_attention_merge_kernel, (unsigned)((long long)n_tokens * head_groups * 16), 128, 0, stream,
+                (const float*)partial, (__nv_bfloat16*)out, (const __nv_bfloat16*)sink, heads, head_groups, rank, n_splits);
+  return launch_status();
+}

@@ -16,20 +16,22 @@ from .lib import DT_BF16, DT_F32, AddTo, LazyNorm, Partials, Prenormed, _check, 
 
 BM, BK = 128, 64
 SPLIT_MAX_ROWS = 256          # steps with more rows never split K
-_lib = None
+_libs = {}
 _error_word: Optional[torch.Tensor] = None
+GLU_DEFINES = {"silu": (), "gelu_tanh": ("-DGLU_GELU_TANH",)}      # the gate's activation is a library's own
 
 
-def lib():
-    global _lib
+def lib(activation: str = "silu"):
+    """The library whose gated products (mode 1) apply `activation` to the gate."""
+    _lib = _libs.get(activation)
     if _lib is None:
-        l = build.load_library("gemm_tcgen05.cu")
+        l = build.load_library("gemm_tcgen05.cu", GLU_DEFINES[activation])
         P, I, L, F = c_void_p, c_int, c_longlong, c_float
         l.llm_gemm_tensor_map.argtypes = [P, P, L, L, L, I]
         l.llm_gemm_tensor_map.restype = c_int
         l.llm_gemm_bf16.argtypes = [P, P, P, I, I, I, I, L, L, I, I, I, I, I, I, P, I, L, F, F, P, L, P, I, P, L, P, P]
         l.llm_gemm_bf16.restype = c_int
-        _lib = l
+        _lib = _libs[activation] = l
     return _lib
 
 
@@ -180,7 +182,7 @@ def takes_prenormed(rows: int, swiglu: bool) -> bool:
 
 
 def run(ctx, plan: GemmPlan, a, rows: int, out_dtype: torch.dtype, buffer: str,
-        allow_partials: bool, swiglu: bool, epilogue=None) -> Optional[Partials]:
+        allow_partials: bool, swiglu: bool, epilogue=None, activation: str = "silu") -> Optional[Partials]:
     """`a`: a bfloat16 matrix, or a `LazyNorm` whose `prenormed` a product before this one left
     (`takes_prenormed` steps only).  `epilogue`: with an `AddTo` whose norm can be prepared, a
     many-token step adds the product into the float32 residual stream itself, leaves bfloat16(new
@@ -200,7 +202,7 @@ def run(ctx, plan: GemmPlan, a, rows: int, out_dtype: torch.dtype, buffer: str,
         raise KernelLaunchError(f"gemm_tcgen05: activations {tuple(a.shape)} {a.dtype} do not fit weight "
                                 f"[{plan.n}, {plan.k}]")
     err = error_word(a.device)
-    l = lib()
+    l = lib(activation if swiglu else "silu")
     code = DT_BF16 if out_dtype == torch.bfloat16 else DT_F32
     if takes_prenormed(rows, swiglu):
         n_out = plan.n // 2 if swiglu else plan.n
@@ -249,7 +251,7 @@ def run(ctx, plan: GemmPlan, a, rows: int, out_dtype: torch.dtype, buffer: str,
         # part, and add the partial results inside the SwiGLU kernel
         from . import lib as K
         full = run(ctx, plan, a, rows, torch.float32, buffer + ".gate_up", True, False)
-        K.swiglu(full, out, rows, ctx.stream)
+        K.glu(full, out, rows, activation, ctx.stream)
         return Partials(out)
     splits = choose_splits(rows, plan.n, plan.k, bn) if (allow_partials and out_dtype == torch.float32) else 1
     if splits > 1:

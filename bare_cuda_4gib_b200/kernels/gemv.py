@@ -21,21 +21,23 @@ PRO_BF16, PRO_NORM, PRO_PRENORMED = 0, 1, 2
 SQ_SLOTS = 32
 EPI_STORE, EPI_ADD, EPI_SWIGLU, EPI_ROPE = 0, 1, 2, 3
 MAX_TOKENS = int(os.environ.get("BARE_CUDA_B200_GEMV_MAX_TOKENS", "24"))     # measured: 24 rows still gain, 32 lose
-_lib = None
+_libs = {}
 _smem: Dict[Tuple[int, int], int] = {}
 
 
-def lib():
-    global _lib
+def lib(activation: str = "silu"):
+    """The library whose gated products apply `activation` to the gate."""
+    from .gemm import GLU_DEFINES
+    _lib = _libs.get(activation)
     if _lib is None:
-        l = build.load_library("gemv_fused.cu")
+        l = build.load_library("gemv_fused.cu", GLU_DEFINES[activation])
         P, I, L, F = c_void_p, c_int, c_longlong, c_float
         l.llm_gemv_fused_smem.argtypes = [I, I]
         l.llm_gemv_fused_smem.restype = L
         l.llm_gemv_fused.argtypes = [P, I, I, I, I, I, P, L, P, I, F, P, P, I, L, I, I, P, P, P, L, I, I, I, I,
                                      P, P, P, I, I, P, I, L, P, L, P, I, P, I, P, P]
         l.llm_gemv_fused.restype = c_int
-        _lib = l
+        _lib = _libs[activation] = l
     return _lib
 
 
@@ -58,7 +60,7 @@ def takes(rows: int, k: int) -> bool:
 
 
 def run(ctx, weight: torch.Tensor, x, rows: int, out_dtype: torch.dtype, buffer: str, swiglu: bool,
-        epilogue) -> Optional[Partials]:
+        epilogue, activation: str = "silu") -> Optional[Partials]:
     """x[:rows] @ weight^T with the input and output forms the kernel fuses.  `x` is a bfloat16
     matrix or a `LazyNorm`; `epilogue` None, `AddTo` or `RotateAndCache`.  Returns the result, or
     None when the epilogue consumed it."""
@@ -96,7 +98,7 @@ def run(ctx, weight: torch.Tensor, x, rows: int, out_dtype: torch.dtype, buffer:
         epi, n_out = EPI_STORE, n
         out = ctx.ws.get(buffer, (rows, n), out_dtype)
     from . import gemm
-    _check(lib().llm_gemv_fused(
+    _check(lib(activation if swiglu else "silu").llm_gemv_fused(
         weight.data_ptr(), n, k, rows, pro, epi, xt.data_ptr(), x_stride, _ptr(norm_w), norm_code, eps,
         _ptr(row_index), out.data_ptr(), DT_BF16 if out.dtype == torch.bfloat16 else DT_F32, out.stride(0), n_out,
         up_offset, cache.k_ptr if cache else 0, cache.v_ptr if cache else 0,

@@ -22,7 +22,10 @@ def lib():
         l.llm_latent_prepare.argtypes = [P, I, L, I, I, I, I, I, I, P, F, P, I, F, P, P, P, L, I, I, P, P, I, I, P]
         l.llm_per_head_linear.argtypes = [P, L, L, P, I, P, L, L, P, L, I, I, I, I, I, P]
         l.llm_latent_attention.argtypes = [P, P, I, P, P, L, I, I, I, I, P, P, P, I, I, F, I, P]
-        for name in ("llm_latent_prepare", "llm_per_head_linear", "llm_latent_attention"):
+        l.llm_latent_attention_mma.argtypes = [P, P, P, P, P, L, I, I, I, I, P, P, P, I, I, F, I, I, P]
+        l.llm_latent_attention_mma_scratch.argtypes = [I, I, I, I]
+        l.llm_latent_attention_mma_scratch.restype = c_longlong
+        for name in ("llm_latent_prepare", "llm_per_head_linear", "llm_latent_attention", "llm_latent_attention_mma"):
             getattr(l, name).restype = c_int
         _lib = l
     return _lib
@@ -57,11 +60,54 @@ def per_head_linear(ctx, x: torch.Tensor, w: torch.Tensor, w_in_rows: bool, out:
         n_out, ctx.stream), "per_head_linear")
 
 
+def mma_takes(dtype: torch.dtype, D: int, rank: int) -> bool:
+    """Whether the tensor-core kernel takes these sizes (else the float32 kernel runs)."""
+    return dtype == torch.bfloat16 and D % 16 == 0 and rank % 32 == 0 and 32 <= rank <= MAX_RANK
+
+
+_scratch = {}      # device -> float32 scratch of the split launches (outgrown ones are kept: graphs hold them)
+_retired = []
+
+
+def _split_scratch(device, floats: int) -> torch.Tensor:
+    buf = _scratch.get(device)
+    if buf is None or buf.numel() < floats:
+        if buf is not None:
+            _retired.append(buf)
+        buf = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        _scratch[device] = buf
+    return buf
+
+
+def key_splits(n_tokens: int, heads: int) -> int:
+    """Thread blocks that share a tile's keys: a step of few tokens (decoding) spreads every token's
+    keys over about two blocks per SM in all.  It depends on the step's shape only, never on the
+    requests' lengths, so a captured graph of the step stays valid while they grow."""
+    from .lib import sm_count
+    tiles = n_tokens * ((heads + 15) // 16)
+    if tiles >= sm_count():
+        return 1
+    return max(1, min(32, (2 * sm_count()) // tiles))
+
+
 def attention(ctx, q_full: torch.Tensor, out: torch.Tensor, cache: CacheView, rank: int, sink: Optional[torch.Tensor],
               heads: int, scale: float, window: int = 0) -> None:
     """out[t, h] = sum_j p_j c_j over the cached vectors [c_j | r_j] at positions <= the query's, p the
     softmax of (q_full[t, h] . [c_j | r_j]) * scale, with exp(sink[h]) in the denominator if given."""
     _dev(q_full, out, sink)
+    if ctx.use_fast_attention and mma_takes(q_full.dtype, cache.head_dim, rank) and cache.dtype == torch.bfloat16:
+        splits = key_splits(ctx.n_tokens, heads)
+        floats = int(lib().llm_latent_attention_mma_scratch(ctx.n_tokens, heads, rank, splits))
+        scratch = _split_scratch(q_full.device, floats).data_ptr() if floats else 0
+        _check(lib().llm_latent_attention_mma(
+            q_full.data_ptr(), out.data_ptr(), scratch, cache.k_ptr, cache.block_table.data_ptr(), cache.page_stride,
+            cache.table_stride, cache.page_tokens, cache.head_dim, rank, _ptr(sink), ctx.positions.data_ptr(),
+            ctx.row_seq.data_ptr(), heads, ctx.n_tokens, float(scale), int(window), splits, ctx.stream),
+            "latent_attention_mma")
+        if splits > 1:
+            from .lib import LAUNCHES
+            LAUNCHES[0] += 1      # the merge is a second kernel
+        return
     _check(lib().llm_latent_attention(
         q_full.data_ptr(), out.data_ptr(), dtype_code(q_full.dtype), cache.k_ptr, cache.block_table.data_ptr(),
         cache.page_stride, cache.table_stride, cache.page_tokens, cache.head_dim, rank, _ptr(sink),

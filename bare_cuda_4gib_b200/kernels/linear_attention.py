@@ -42,8 +42,9 @@ _retired = []
 
 def _stretches(ctx, q, heads: int, dk: int, dv: int) -> int:
     """How many stretches a step's longest portion is cut into (1: walked in one piece).  Only
-    bfloat16 steps are cut: the pieces' sums are joined in another order than one walk forms them."""
-    if q.dtype != torch.bfloat16 or ctx.max_q_len < STRETCHES_FROM:
+    bfloat16 steps are cut (also where the scan's operands are float32 copies): the pieces' sums are
+    joined in another order than one walk forms them."""
+    if ctx.dtype != torch.bfloat16 or ctx.max_q_len < STRETCHES_FROM:
         return 1
     n = -(-ctx.max_q_len // STRETCH)
     if ctx.n_seqs * n * heads * (dk * dv + dk) * 4 > STRETCH_SCRATCH_BYTES or (dk * dv + 32 * dk) * 4 > 160 * 1024:

@@ -40,33 +40,23 @@ class Linear:
         do with the result next: a kernel that can do it itself does, and None comes back; from
         every other kernel the plain result comes back and the epilogue stays the caller's.
         `glu` names the activation of a gated product ("silu" is what `swiglu` asks for)."""
-        if glu is not None and glu != "silu":
-            return self._glu(ctx, a, rows, out_dtype, buffer, glu)
-        swiglu = swiglu or glu == "silu"
+        activation = glu or "silu"
+        swiglu = swiglu or glu is not None
         width = self.out_features // 2 if swiglu else self.out_features
         if self.few and ctx.use_fast_gemm:
             from ..kernels import gemv
             if gemv.takes(rows, self.in_features):
-                return gemv.run(ctx, self.weight, a, rows, out_dtype, buffer, swiglu, epilogue)
+                return gemv.run(ctx, self.weight, a, rows, out_dtype, buffer, swiglu, epilogue, activation)
         if self.fast is not None and ctx.use_fast_gemm:
             from ..kernels import gemm
-            return gemm.run(ctx, self.fast, a, rows, out_dtype, buffer, allow_partials, swiglu, epilogue)
+            return gemm.run(ctx, self.fast, a, rows, out_dtype, buffer, allow_partials, swiglu, epilogue, activation)
         a = K.materialize(a)
         if swiglu:
             full = ctx.ws.get(buffer + ".gate_up", (rows, self.out_features), out_dtype)
             K.matmul_plain(a, self.weight, full, rows, ctx.stream)
             out = ctx.ws.get(buffer, (rows, width), out_dtype)
-            K.swiglu(K.Partials(full), out, rows, ctx.stream)
+            K.glu(K.Partials(full), out, rows, activation, ctx.stream)
             return K.Partials(out)
         out = ctx.ws.get(buffer, (rows, width), out_dtype)
         K.matmul_plain(a, self.weight, out, rows, ctx.stream)
-        return K.Partials(out)
-
-    def _glu(self, ctx, a, rows: int, out_dtype: torch.dtype, buffer: str, activation: str) -> K.Partials:
-        """W = [gate; up]: activation(gate) * up, the product first and the activation as a kernel of
-        its own over its (partial) sums."""
-        full = self.forward(ctx, a, rows, torch.float32 if rows <= 256 else out_dtype, buffer + ".gate_up",
-                            allow_partials=True)
-        out = ctx.ws.get(buffer, (rows, self.out_features // 2), out_dtype)
-        K.glu(full, out, rows, activation, ctx.stream)
         return K.Partials(out)

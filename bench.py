@@ -186,7 +186,7 @@ SETTLE_SECONDS = 0.1      # pause between putting the prompts into the cache and
 
 
 def design_main(args) -> int:
-    """`--design dopudra`: one JSON line with, per size, a prefill step of `--prefill-tokens` tokens and decode
+    """`--design dopudra` or `--design zadurax`: one JSON line with, per size, a prefill step of `--prefill-tokens` tokens and decode
     steps at `--batch` requests of `--context` positions for the design and for the Llama decoder of the same
     width, both with `--design-layers` layers, seeded random weights, bfloat16, CUDA events around the steps."""
     import torch
@@ -257,7 +257,7 @@ def design_main(args) -> int:
                 "weight_bytes": weights}
 
     sizes = []
-    for name, closest in (("dopudra-2048", "tinyllama"), ("dopudra-4096", "llama2-7b")):
+    for name, closest in ((f"{args.design}-2048", "tinyllama"), (f"{args.design}-4096", "llama2-7b")):
         if args.preset not in ("tinyllama", name):       # --preset NAME: that size only
             continue
         layers = PRESETS[name]["layers"][: args.design_layers]
@@ -288,7 +288,7 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--only", default="", choices=["", "prefill", "decode"],
                     help="profiling aid: run just the prefill step or just the decode steps and print their time")
-    ap.add_argument("--design", default="", choices=["", "dopudra"],
+    ap.add_argument("--design", default="", choices=["", "dopudra", "zadurax"],
                     help="instead of the default workload: prefill and decode throughput of this design at layer sizes "
                          "of real models, beside the Llama decoder at equal width, layer count and vocabulary")
     ap.add_argument("--design-layers", type=int, default=8, help="layers of both models in a --design run")

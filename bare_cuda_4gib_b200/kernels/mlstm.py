@@ -21,7 +21,8 @@ def lib():
         l.llm_mlstm_gates.argtypes = [P, L, I, I, P, P, I, F, P, P, P, P, P, I, I, P]
         l.llm_mlstm_operands.argtypes = [P, I, L, I, I, I, P, P, P, P, P, I, I, I, I, I, P]
         l.llm_mlstm_finish.argtypes = [P, P, P, P, L, P, L, I, I, I, I, I, F, P]
-        for name in ("llm_mlstm_gates", "llm_mlstm_operands", "llm_mlstm_finish"):
+        l.llm_mlstm_step.argtypes = [P, I, L, I, I, I, I, P, L, I, I, P, P, F, P, P, P, P, L, P, P, P, I, I, I, I, I, F, F, P]
+        for name in ("llm_mlstm_gates", "llm_mlstm_operands", "llm_mlstm_finish", "llm_mlstm_step"):
             getattr(l, name).restype = c_int
         _lib = l
     return _lib
@@ -55,3 +56,26 @@ def finish(ctx, scanned: torch.Tensor, coef: torch.Tensor, norm_w: torch.Tensor,
     _check(lib().llm_mlstm_finish(scanned.data_ptr(), coef.data_ptr(), norm_w.data_ptr(), gate.data_ptr(),
                                   gate.stride(0), out.data_ptr(), out.stride(0), dtype_code(out.dtype), ctx.n_tokens,
                                   heads, dv, dvp, float(eps), ctx.stream), "mlstm_finish")
+
+
+STEP_MAX_VALUE_COLUMNS = 288      # vdim + pad the one-token kernel keeps per warp
+STEP_MAX_SHARED = 48 * 1024
+
+
+def step_takes(dk: int, dvp: int) -> bool:
+    return dvp <= STEP_MAX_VALUE_COLUMNS and (2 * dk + 9 * dvp + 8) * 4 <= STEP_MAX_SHARED
+
+
+def step(ctx, u: torch.Tensor, q_col: int, k_col: int, v_col: int, g_col: int, z: torch.Tensor, i_col: int, f_col: int,
+         i_bias: torch.Tensor, f_bias: torch.Tensor, cap: float, state: torch.Tensor, m_state: torch.Tensor,
+         norm_w: torch.Tensor, out: torch.Tensor, heads: int, dk: int, dv: int, dvp: int, q_scale: float, eps: float) -> None:
+    """All of a head's work for a step of one token per request: gates, m, [S | n] updated in place,
+    quotient, unit norm, weight and gate."""
+    _dev(u, z, i_bias, f_bias, state, m_state, norm_w, out)
+    if z.dtype != torch.float32 or state.dtype != torch.float32 or m_state.dtype != torch.float32:
+        raise TypeError("mlstm step: gate projections and states must be float32")
+    _check(lib().llm_mlstm_step(u.data_ptr(), dtype_code(u.dtype), u.stride(0), q_col, k_col, v_col, g_col, z.data_ptr(),
+                                z.stride(0), i_col, f_col, i_bias.data_ptr(), f_bias.data_ptr(), float(cap),
+                                state.data_ptr(), m_state.data_ptr(), norm_w.data_ptr(), out.data_ptr(), out.stride(0),
+                                ctx.seq_slot.data_ptr(), ctx.seq_q_start.data_ptr(), ctx.seq_q_len.data_ptr(), ctx.n_seqs,
+                                heads, dk, dv, dvp, float(q_scale), float(eps), ctx.stream), "mlstm_step")

@@ -76,6 +76,12 @@ class MLSTM(Part):
         kd, vd = H * dk, H * dv
         u = self.proj.forward(ctx, h, n, ctx.dtype, "mixer_in").tensor
         z = self.gates.forward(ctx, h, n, torch.float32, "mlstm_gates").tensor
+        out = ctx.ws.get("mixer_act", (n, vd), ctx.dtype)
+        if ctx.max_q_len == 1 and MK.step_takes(dk, dvp):
+            # one token per request: one kernel per step instead of gates, operands, scan and finish
+            MK.step(ctx, u, 0, kd, 2 * kd, 2 * kd + vd, z, 0, H, self.i_bias, self.f_bias, self.cap, call.states[0],
+                    call.states[1], self.norm_w, out, H, dk, dv, dvp, dk ** -0.5, self.eps)
+            return self.o.forward(ctx, out, n, torch.float32, "mixer_out", allow_partials=True)
         coef = ctx.ws.get("mlstm_coef", (n, H * 4), torch.float32)
         MK.gates(ctx, z, 0, H, self.i_bias, self.f_bias, self.cap, call.states[1], coef, H)
         qf = ctx.ws.get("mlstm_q", (n, kd), torch.float32)
@@ -85,6 +91,5 @@ class MLSTM(Part):
         MK.operands(ctx, u, 0, kd, 2 * kd, coef, qf, kf, decay, vf, H, dk, dv, dvp)
         scanned = ctx.ws.get("mlstm_scan", (n, H * dvp), torch.float32)
         LA.scan(ctx, qf, kf, vf, decay, True, call.states[0], scanned, H, dk, dvp, dk ** -0.5)
-        out = ctx.ws.get("mixer_act", (n, vd), ctx.dtype)
         MK.finish(ctx, scanned, coef, self.norm_w, u[:, 2 * kd + vd:], out, H, dv, dvp, self.eps)
         return self.o.forward(ctx, out, n, torch.float32, "mixer_out", allow_partials=True)

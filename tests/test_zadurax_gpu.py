@@ -42,6 +42,11 @@ ALONE = {
     "latent": [Z.latent(3, 12, 8, 20, 24, 0.2, scaling=Z.yarn(4.0, 64, 16.0, 2.0))],
     "latent_plain_frequencies": [Z.latent(1, 40, 4, 8, 33, 0.1, base=50.0)],
     "latent_many_heads": [Z.latent(11, 8, 6, 4, 16, 0.4, scaling=Z.yarn(8.0, 32, 8.0, 1.0), ff=56)],
+    # sizes the tensor-core kernel takes in bfloat16: fewer heads than a tile has rows; two tiles of heads and
+    # key blocks of 64; a cached vector so wide that key blocks are 32
+    "latent_tensor_cores": [Z.latent(5, 16, 16, 8, 32, 0.2, scaling=Z.yarn(4.0, 64, 16.0, 2.0))],
+    "latent_two_tiles_of_heads": [Z.latent(18, 8, 32, 8, 96, 0.15, base=1000.0)],
+    "latent_wide": [Z.latent(2, 8, 32, 8, 256, 0.1, scaling=Z.yarn(2.0, 32, 4.0, 1.0))],
     "mlstm": [Z.mlstm(3, 8, 20, 15.0)],
     "mlstm_one_head_tight_gates": [Z.mlstm(1, 40, 12, 1.5, ff=48)],
     "mlstm_wide": [Z.mlstm(2, 64, 64, 30.0)],
@@ -227,7 +232,7 @@ def _moved(folder, cfg, ids, other, at):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_far_key_in_the_latent_cache_decides(dtype):
-    folder, cfg = _planted(Z.latent(2, 32, 8, 16, 48, 0.25, scaling=Z.yarn(4.0, 64, 16.0, 2.0)), 21, "latent")
+    folder, cfg = _planted(Z.latent(2, 32, 16, 16, 64, 0.25, scaling=Z.yarn(4.0, 64, 16.0, 2.0)), 21, "latent")
     rng = random.Random(2)
     filler = lambda n: [rng.randrange(2, cfg["vocab"]) for _ in range(n)]
     ids = filler(9) + [0] + filler(290) + [1] + filler(3)      # the far key is 291 positions back, pages away
@@ -251,7 +256,7 @@ def test_the_sink_takes_its_share(dtype):
     ids = H.random_ids(rng, 40, 53)
     logits = {}
     for sink in (-30.0, 2.0, 30.0):
-        folder, cfg = _planted(Z.latent(2, 32, 8, 16, 48, 0.25), 22, f"sink{sink}", sink=sink)
+        folder, cfg = _planted(Z.latent(2, 32, 16, 16, 64, 0.25), 22, f"sink{sink}", sink=sink)
         logits[sink] = Z.plain_logits(folder, ids)
         got = H.Replayer(folder, dtype, 16, 48).run(H.trace_whole({"p": ids}))
         Z.check(folder, {"p": ids}, got, dtype)
@@ -409,7 +414,7 @@ def _random_config(seed):
     def latent():
         rot = pick([2, 4, 8, 16, 32])
         scaling = pick([None, Z.yarn(pick([2.0, 8.0, 40.0]), pick([16, 64, 1000]), pick([4.0, 32.0]), pick([0.5, 1.0, 2.0]))])
-        return Z.latent(pick([1, 2, 3, 5, 9]), pick([4, 8, 12, 32, 64]), rot, pick([4, 8, 20, 64]), pick([8, 16, 24, 50, 96]),
+        return Z.latent(pick([1, 2, 3, 5, 9, 17]), pick([4, 8, 12, 32, 64]), rot, pick([4, 8, 20, 64]), pick([8, 24, 32, 50, 64, 96]),
                         pick([0.05, 0.125, 0.3]), base=pick([100.0, 50000.0]), scaling=scaling, ff=ff())
 
     def mlstm():

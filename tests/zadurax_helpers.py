@@ -54,7 +54,7 @@ def _cfg_p():
 
 
 def _cfg_q():
-    layers = [latent(2, 24, 16, 8, 40, 0.15, base=100.0, ff=64),            # no scaling of the frequencies
+    layers = [latent(2, 24, 16, 8, 64, 0.15, base=100.0, ff=64),            # no scaling of the frequencies
               attention(2, 2, 64, 40, 64, base=500.0, scale=0.1),            # as many key heads as heads, all entries turned
               mlstm(1, 32, 8, 6.0, ff=72),
               attention(6, 1, 32, 1000, 2, ff=40)]                           # a window wider than any request

@@ -599,6 +599,219 @@ latent_attention_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* 
   }
 }
 
+// The same attention for prompt portions whose latent has at most 256 entries.  A tile is four tokens
+// of one request in a row, a warp one token's 16 heads; the four warps share the cached blocks in
+// shared memory (a quarter of the reads of the kernel above) and nothing else: a warp scores all 32
+// keys of a block for its rows, keeps its running maxima and sums in registers, turns its score
+// fragments into the weights' operand fragments where they are, and adds into its own O (all value
+// columns).  Keys from the first one that the tile's first token may see to the last token's own; a
+// warp masks what its token may not see.  Grid (request x ceil(longest portion / 4), group of 16 heads).
+template <int NT_MAX>
+__global__ void __launch_bounds__(LM_THREADS, NT_MAX > 16 ? 2 : 3)
+latent_attention_rows_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, PagedCache cache,
+                             int rank, const __nv_bfloat16* __restrict__ sink, const int32_t* __restrict__ positions,
+                             const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_q_len,
+                             const int32_t* __restrict__ row_seq, int heads, int tiles_per_seq, float scale_log2,
+                             int window) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int KB = 32;
+  extern __shared__ __align__(16) uint8_t lm_smem[];
+  const int D = cache.head_dim, ld = D + 8, chunks = D / 8;
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(lm_smem);      // [64][ld]: warp w's rows are 16 w ..
+  __nv_bfloat16* ks = qs + 64 * ld;                                   // [2][KB][ld]
+  long long* koff = reinterpret_cast<long long*>(ks + 2 * KB * ld);   // [3][KB]: the warps run up to a block apart
+  const int seq = blockIdx.x / tiles_per_seq, tok0 = (blockIdx.x - seq * tiles_per_seq) * 4, hg = blockIdx.y;
+  const int q_len = seq_q_len[seq];
+  if (tok0 >= q_len) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row0 = seq_q_start[seq] + tok0;
+  const int last = min(3, q_len - 1 - tok0);                // the tile's last token
+  const int pos0 = positions[row0], pos_hi = pos0 + last;
+  const int cache_seq = row_seq[row0];
+  const bool mine = warp <= last;
+  const int pos = pos0 + warp;                              // positions of a request's tokens follow one another
+  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int b0 = first_lo / KB, b1 = pos_hi / KB + 1;
+  const __nv_bfloat16* kc = (const __nv_bfloat16*)cache.k;
+
+  for (int idx = threadIdx.x; idx < 64 * chunks; idx += LM_THREADS) {
+    const int r = idx / chunks, c = idx - r * chunks, w = r >> 4, h = hg * 16 + (r & 15);
+    const bool valid = h < heads && w <= last;
+    cp_async_16_or_zero(qs + r * ld + c * 8, q + ((row0 + (valid ? w : 0)) * heads + (valid ? h : 0)) * D + c * 8, valid);
+  }
+  auto offsets = [&](int b, int slot) {
+    if (threadIdx.x < KB) {
+      const int j = b * KB + threadIdx.x;
+      long long off = -1;
+      if (j >= first_lo && j <= pos_hi) {
+        const int page = cache.block_table[(long long)cache_seq * cache.table_stride + j / cache.page_tokens];
+        if (page >= 0) off = (long long)page * cache.page_stride + (long long)(j % cache.page_tokens) * D;
+      }
+      koff[slot * KB + threadIdx.x] = off;
+    }
+  };
+  auto copies = [&](int stage, int slot) {
+    __nv_bfloat16* dst = ks + stage * KB * ld;
+    for (int idx = threadIdx.x; idx < KB * chunks; idx += LM_THREADS) {
+      const int kk = idx / chunks, c = idx - kk * chunks;
+      const long long off = koff[slot * KB + kk];
+      cp_async_16_or_zero(dst + kk * ld + c * 8, kc + (off >= 0 ? off : 0) + c * 8, off >= 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  offsets(b0, 0);
+  __syncthreads();
+  copies(0, 0);
+
+  const int r0 = lane >> 2, cq = (lane & 3) * 2;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+  float o[NT_MAX][4];
+#pragma unroll
+  for (int i = 0; i < NT_MAX; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  const int ntw = rank / 8;
+  const __nv_bfloat16* qw = qs + warp * 16 * ld;
+
+  for (int b = b0; b < b1; ++b) {
+    const int stage = (b - b0) & 1, slot = (b - b0) % 3, next = (b - b0 + 1) % 3;
+    if (b + 1 < b1) offsets(b + 1, next);      // a slot that no warp still reads: they are at most one block behind
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (b + 1 < b1) copies(stage ^ 1, next);
+    if (!mine || b * KB > pos || (b + 1) * KB <= first) continue;      // nothing in this block for this warp's token
+    const __nv_bfloat16* kb = ks + stage * KB * ld;
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+    for (int k0 = 0; k0 < D; k0 += 16) {
+      uint32_t a[4], b01[4], b23[4];
+      ldsm_x4(a, qw + (lane & 15) * ld + k0 + (lane >> 4) * 8);
+      const __nv_bfloat16* kp = kb + ((lane & 7) + ((lane >> 4) & 1) * 8) * ld + k0 + ((lane >> 3) & 1) * 8;
+      ldsm_x4(b01, kp);
+      ldsm_x4(b23, kp + 16 * ld);
+      mma_bf16(s[0], a, b01[0], b01[1]);
+      mma_bf16(s[1], a, b01[2], b01[3]);
+      mma_bf16(s[2], a, b23[0], b23[1]);
+      mma_bf16(s[3], a, b23[2], b23[3]);
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = i * 8 + cq + (e & 1), j = b * KB + key;
+        const float v = (koff[slot * KB + key] >= 0 && j >= first && j <= pos) ? s[i][e] * scale_log2 : -INFINITY;
+        s[i][e] = v;
+        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+      }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    if (n0 == -INFINITY && n1 == -INFINITY) continue;
+    const float c0 = n0 == -INFINITY ? 1.0f : exp2f(m0 - n0), c1 = n1 == -INFINITY ? 1.0f : exp2f(m1 - n1);
+    float sum0 = 0.0f, sum1 = 0.0f;
+    uint32_t pa[2][4];       // the weights as the A operand of P V: keys 0..15 and 16..31
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float p0 = n0 == -INFINITY ? 0.0f : exp2f(s[i][0] - n0), p1 = n0 == -INFINITY ? 0.0f : exp2f(s[i][1] - n0);
+      const float p2 = n1 == -INFINITY ? 0.0f : exp2f(s[i][2] - n1), p3 = n1 == -INFINITY ? 0.0f : exp2f(s[i][3] - n1);
+      sum0 += p0 + p1;
+      sum1 += p2 + p3;
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1), hi = __floats2bfloat162_rn(p2, p3);
+      pa[i >> 1][(i & 1) * 2] = *reinterpret_cast<const uint32_t*>(&lo);
+      pa[i >> 1][(i & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+    }
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+    l0 = l0 * c0 + sum0;
+    l1 = l1 * c1 + sum1;
+    m0 = n0;
+    m1 = n1;
+#pragma unroll
+    for (int i = 0; i < NT_MAX; ++i)
+      if (i < ntw) {
+        o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
+      }
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+      const __nv_bfloat16* vrow = kb + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + ((lane >> 4) & 1) * 8;
+#pragma unroll
+      for (int i = 0; i < NT_MAX; i += 2)
+        if (i < ntw) {
+          uint32_t bb[4];
+          ldsm_x4_trans(bb, vrow + i * 8);
+          mma_bf16(o[i], pa[kk], bb[0], bb[1]);
+          mma_bf16(o[i + 1], pa[kk], bb[2], bb[3]);
+        }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (!mine) return;
+  const int h0 = hg * 16 + r0, h1 = h0 + 8;
+  if (sink) {
+    if (h0 < heads) {
+      const float sk = __bfloat162float(sink[h0]) * 1.4426950408889634f, n = fmaxf(m0, sk);
+      const float c = m0 == -INFINITY ? 0.0f : exp2f(m0 - n);
+      l0 = l0 * c + exp2f(sk - n);
+#pragma unroll
+      for (int i = 0; i < NT_MAX; ++i) { o[i][0] *= c; o[i][1] *= c; }
+    }
+    if (h1 < heads) {
+      const float sk = __bfloat162float(sink[h1]) * 1.4426950408889634f, n = fmaxf(m1, sk);
+      const float c = m1 == -INFINITY ? 0.0f : exp2f(m1 - n);
+      l1 = l1 * c + exp2f(sk - n);
+#pragma unroll
+      for (int i = 0; i < NT_MAX; ++i) { o[i][2] *= c; o[i][3] *= c; }
+    }
+  }
+  const float i0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, i1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+  const long long t = row0 + warp;
+#pragma unroll
+  for (int i = 0; i < NT_MAX; ++i)
+    if (i < ntw) {
+      const int c = i * 8 + cq;
+      if (h0 < heads)
+        *reinterpret_cast<__nv_bfloat162*>(out + (t * heads + h0) * rank + c) = __floats2bfloat162_rn(o[i][0] * i0, o[i][1] * i0);
+      if (h1 < heads)
+        *reinterpret_cast<__nv_bfloat162*>(out + (t * heads + h1) * rank + c) = __floats2bfloat162_rn(o[i][2] * i1, o[i][3] * i1);
+    }
+}
+
+extern "C" int llm_latent_attention_rows(const void* q, void* out, void* k_base, const int32_t* block_table,
+                                         long long page_stride, int table_stride, int page_tokens, int D, int rank,
+                                         const void* sink, const int32_t* positions, const int32_t* seq_q_start,
+                                         const int32_t* seq_q_len, const int32_t* row_seq, int heads, int n_seqs,
+                                         int max_q_len, float scale, int window, cudaStream_t stream) {
+  if (n_seqs <= 0 || max_q_len <= 0) return 0;
+  LLM_HOST_CHECK(D % 16 == 0 && rank % 16 == 0 && rank >= 16 && rank <= 256 && rank <= D, ERR_BAD_SIZE);
+  LLM_HOST_CHECK(((uintptr_t)q % 16) == 0 && ((uintptr_t)k_base % 16) == 0 && page_stride % 8 == 0, ERR_BAD_ALIGN);
+  PagedCache c{k_base, k_base, block_table, page_stride, table_stride, page_tokens, 1, D};
+  const int tiles_per_seq = (max_q_len + 3) / 4, head_groups = (heads + 15) / 16;
+  const size_t smem = (size_t)(64 + 2 * 32) * (D + 8) * 2 + (size_t)3 * 32 * sizeof(long long);
+  LLM_HOST_CHECK(smem <= 200 * 1024, ERR_BAD_SIZE);
+  dim3 grid((unsigned)((long long)n_seqs * tiles_per_seq), head_groups);
+  LLM_HOST_CHECK(head_groups <= 65535, ERR_BAD_SIZE);
+  const float scale_log2 = scale * 1.4426950408889634f;
+#define GO(NT)                                                                                                       \
+  do {                                                                                                               \
+    auto kernel = latent_attention_rows_kernel<NT>;                                                                  \
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                            \
+    launch_kernel(kernel, grid, LM_THREADS, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, c, rank,     \
+                  (const __nv_bfloat16*)sink, positions, seq_q_start, seq_q_len, row_seq, heads, tiles_per_seq,      \
+                  scale_log2, window);                                                                               \
+  } while (0)
+  if (rank <= 64) GO(8);
+  else if (rank <= 128) GO(16);
+  else GO(32);
+#undef GO
+  return launch_status();
+}
+
 // Floats of scratch a launch with these splits needs.
 extern "C" long long llm_latent_attention_mma_scratch(int n_tokens, int heads, int rank, int n_splits) {
   return n_splits > 1 ? (long long)n_tokens * ((heads + 15) / 16) * n_splits * 16 * (rank + 2) : 0;

@@ -22,6 +22,7 @@
 
 #define DECAY_PER_HEAD 0
 #define DECAY_PER_CHANNEL 1
+#define DECAY_PER_TOKEN 2      // one number per (token, head), the same for every key channel: decay [tokens][heads]
 
 __device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
@@ -67,7 +68,7 @@ template <typename T, int DECAY, int ROWS, bool VEC>
 __global__ void __launch_bounds__(SCAN_THREADS)
 linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                              long long q_stride, long long k_stride, long long v_stride,
-                             const float* __restrict__ decay,          // [heads] or [tokens][heads * dk]
+                             const float* __restrict__ decay,          // [heads], [tokens][heads * dk] or [tokens][heads]
                              float* __restrict__ state,                // [slots][heads][dk][dv]
                              float* __restrict__ out,                  // [tokens][heads * dv]
                              const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_q_start,
@@ -91,7 +92,7 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
   const int n_cols = min(cols_per_block, dv - col0);
   const int tok = 2 * dk + cols_per_block;                 // elements of T per token in a buffer
   const int t_bytes = (chunk * tok * (int)sizeof(T) + 15) & ~15;
-  const int buf_bytes = t_bytes + (DECAY == DECAY_PER_CHANNEL ? chunk * dk * 4 : 0);
+  const int buf_bytes = t_bytes + (DECAY == DECAY_PER_CHANNEL ? chunk * dk * 4 : DECAY == DECAY_PER_TOKEN ? ((chunk * 4 + 15) & ~15) : 0);
   pdl_wait();
   const int n_all = seq_q_len[seq];
   const int seg_first = n_segs > 1 ? seg * seg_len : 0;
@@ -108,7 +109,7 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
   }
   // a later stretch also leaves, per token, the product of the decays from its start (one thread group
   // per head does: the first value column's)
-  const bool keeps_cum = DECAY == DECAY_PER_CHANNEL && n_segs > 1 && seg > 0 && col == 0;
+  const bool keeps_cum = DECAY != DECAY_PER_HEAD && n_segs > 1 && seg > 0 && col == 0;
   float cp[ROWS];
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) cp[r] = 1.0f;
@@ -145,6 +146,9 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
         }
       }
     }
+    if (DECAY == DECAY_PER_TOKEN && threadIdx.x < count)
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dec + threadIdx.x)),
+                   "l"(decay + (row0 + first + threadIdx.x) * (long long)heads + head) : "memory");
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
@@ -168,6 +172,7 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
     // tokens in groups: a group's loads and products are independent of one another but for the one
     // multiply-add per state element that carries the state on, and its reductions run side by side
     constexpr int GROUP = DECAY == DECAY_PER_CHANNEL ? 2 : 4;
+    const int token_decay = DECAY == DECAY_PER_TOKEN;
     const int at = valid > 0 ? kr * ROWS : 0;
     auto token = [&](int t) -> float {
       const T* w = raw + t * tok;
@@ -175,8 +180,14 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
       float qq[ROWS], kk[ROWS], aa[ROWS];
       load_rows<T, ROWS, VEC>(w + at, valid, qq);
       load_rows<T, ROWS, VEC>(w + dk + at, valid, kk);
-      if (DECAY == DECAY_PER_CHANNEL) {
-        load_rows<float, ROWS, VEC>(dec + t * dk + at, valid, aa);
+      if (DECAY != DECAY_PER_HEAD) {
+        if (token_decay) {
+          const float a = dec[t];
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r) aa[r] = a;
+        } else {
+          load_rows<float, ROWS, VEC>(dec + t * dk + at, valid, aa);
+        }
         if (keeps_cum) {
           float* c_row = cum + (long long)(row0 + first + t) * ((long long)heads * dk) + head * dk + kr * ROWS;
 #pragma unroll
@@ -189,7 +200,7 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
       float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) {
-        const float a = DECAY == DECAY_PER_CHANNEL ? aa[r] : head_decay;
+        const float a = DECAY != DECAY_PER_HEAD ? aa[r] : head_decay;
         S[r] = a * S[r] + kk[r] * vv;
         part[r & 3] += S[r] * qq[r];
       }
@@ -368,6 +379,7 @@ extern "C" int llm_linear_attention_scan(const void* q, const void* k, const voi
                                          int dk, int dv, float q_scale, int seg_len, int n_segs, float* seg_state,
                                          float* seg_decay, float* cum, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
+  LLM_HOST_CHECK(per_channel >= 0 && per_channel <= 2, ERR_BAD_SIZE);
   LLM_HOST_CHECK(n_segs >= 1 && (n_segs == 1 || (seg_len > 0 && seg_len % CORRECT_TOKENS == 0 && seg_state &&
                                                  (!per_channel || (seg_decay && cum)))), ERR_BAD_SIZE);
   LLM_HOST_CHECK(dk >= 1 && dk <= 256 && dv >= 1 && heads >= 1 && heads <= 65535, ERR_BAD_SIZE);
@@ -378,16 +390,17 @@ extern "C" int llm_linear_attention_scan(const void* q, const void* k, const voi
   const int cols_per_block = (32 / ks) * SCAN_WARPS;
   const int slices = (dv + cols_per_block - 1) / cols_per_block;
   const int esize = dtype == DT_F32 ? 4 : 2;
-  const int token_bytes = (2 * dk + cols_per_block) * esize + (per_channel ? dk * 4 : 0);
+  const int token_bytes = (2 * dk + cols_per_block) * esize + (per_channel == 1 ? dk * 4 : per_channel == 2 ? 4 : 0);
   int chunk = 16;
   while (chunk > 2 && chunk * token_bytes > 16 * 1024) chunk >>= 1;
-  const size_t smem = SCAN_BUFFERS * (size_t)(((chunk * (2 * dk + cols_per_block) * esize + 15) & ~15) + (per_channel ? chunk * dk * 4 : 0));
+  const size_t smem = SCAN_BUFFERS * (size_t)(((chunk * (2 * dk + cols_per_block) * esize + 15) & ~15) +
+                                              (per_channel == 1 ? chunk * dk * 4 : per_channel == 2 ? ((chunk * 4 + 15) & ~15) : 0));
   LLM_HOST_CHECK(smem <= 200 * 1024, ERR_BAD_SIZE);
   // 16-byte copies need every head slice of every row to start and end on a 16-byte boundary
   const int per = 16 / esize;
   auto ok = [&](const void* p, long long stride) { return ((uintptr_t)p % 16) == 0 && stride % per == 0; };
   int aligned = ok(q, q_stride) && ok(k, k_stride) && ok(v, v_stride) && dk % per == 0 && dv % per == 0 &&
-                cols_per_block % per == 0 && (!per_channel || (dk % 4 == 0 && ((uintptr_t)decay % 16) == 0));
+                cols_per_block % per == 0 && (per_channel != 1 || (dk % 4 == 0 && ((uintptr_t)decay % 16) == 0));
   dim3 grid(n_seqs, heads, slices * n_segs);
   LLM_HOST_CHECK(grid.z <= 65535, ERR_BAD_SIZE);
   // 16-byte loads of a thread's rows from shared memory: the threads' rows cover the key size exactly, and
@@ -404,10 +417,12 @@ extern "C" int llm_linear_attention_scan(const void* q, const void* k, const voi
                                             chunk, aligned, q_scale, seg_len, n_segs, slices, seg_state, seg_decay, cum); \
   } while (0)
   if (dtype == DT_F32) {
-    if (per_channel) { if (rows == 8) GO(float, 1, 8); else GO(float, 1, 16); }
+    if (per_channel == 2) { if (rows == 8) GO(float, 2, 8); else GO(float, 2, 16); }
+    else if (per_channel) { if (rows == 8) GO(float, 1, 8); else GO(float, 1, 16); }
     else { if (rows == 8) GO(float, 0, 8); else GO(float, 0, 16); }
   } else {
-    if (per_channel) { if (rows == 8) GO(__nv_bfloat16, 1, 8); else GO(__nv_bfloat16, 1, 16); }
+    if (per_channel == 2) { if (rows == 8) GO(__nv_bfloat16, 2, 8); else GO(__nv_bfloat16, 2, 16); }
+    else if (per_channel) { if (rows == 8) GO(__nv_bfloat16, 1, 8); else GO(__nv_bfloat16, 1, 16); }
     else { if (rows == 8) GO(__nv_bfloat16, 0, 8); else GO(__nv_bfloat16, 0, 16); }
   }
 #undef GO

@@ -86,7 +86,7 @@ extern "C" int llm_mlstm_gates(const float* z, long long z_stride, int i_col, in
   return launch_status();
 }
 
-// Grid (token, head): the scan's float32 operands.  qf = q, kf = b k, decay = a on every key channel,
+// Grid (token, head): the scan's float32 operands.  qf = q, kf = b k, decay[token][head] = a,
 // vf = [v | 1 | 0 ...] (dvp columns per head).
 template <typename T>
 __global__ void mlstm_operands_kernel(const T* __restrict__ u, long long u_stride, int q_col, int k_col, int v_col,
@@ -100,10 +100,10 @@ __global__ void mlstm_operands_kernel(const T* __restrict__ u, long long u_strid
   const float4 c = coef[t * heads + h];
   const T* row = u + t * u_stride;
   const long long kbase = (t * heads + h) * dk, vbase = (t * heads + h) * dvp;
+  if (threadIdx.x == 0) decay[t * heads + h] = c.x;
   for (int i = threadIdx.x; i < dk; i += blockDim.x) {
     qf[kbase + i] = to_float(row[q_col + h * dk + i]);
     kf[kbase + i] = c.y * to_float(row[k_col + h * dk + i]);
-    decay[kbase + i] = c.x;
   }
   for (int i = threadIdx.x; i < dvp; i += blockDim.x)
     vf[vbase + i] = i < dv ? to_float(row[v_col + h * dv + i]) : (i == dv ? 1.0f : 0.0f);

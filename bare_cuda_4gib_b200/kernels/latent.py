@@ -11,6 +11,7 @@ from . import build
 from .lib import CacheView, _check, _dev, _ptr, dtype_code
 
 MAX_RANK = 512      # value entries the attention kernel keeps per lane times 32
+ROWS_KERNEL_FROM = 8      # steps whose longest portion has at least this many tokens run the kernel for portions
 _lib = None
 
 
@@ -25,7 +26,9 @@ def lib():
         l.llm_latent_attention_mma.argtypes = [P, P, P, P, P, L, I, I, I, I, P, P, P, I, I, F, I, I, P]
         l.llm_latent_attention_mma_scratch.argtypes = [I, I, I, I]
         l.llm_latent_attention_mma_scratch.restype = c_longlong
-        for name in ("llm_latent_prepare", "llm_per_head_linear", "llm_latent_attention", "llm_latent_attention_mma"):
+        l.llm_latent_attention_rows.argtypes = [P, P, P, P, L, I, I, I, I, P, P, P, P, P, I, I, I, F, I, P]
+        for name in ("llm_latent_prepare", "llm_per_head_linear", "llm_latent_attention", "llm_latent_attention_mma",
+                     "llm_latent_attention_rows"):
             getattr(l, name).restype = c_int
         _lib = l
     return _lib
@@ -95,6 +98,15 @@ def attention(ctx, q_full: torch.Tensor, out: torch.Tensor, cache: CacheView, ra
     """out[t, h] = sum_j p_j c_j over the cached vectors [c_j | r_j] at positions <= the query's, p the
     softmax of (q_full[t, h] . [c_j | r_j]) * scale, with exp(sink[h]) in the denominator if given."""
     _dev(q_full, out, sink)
+    if (ctx.use_fast_attention and q_full.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
+            and ctx.max_q_len >= ROWS_KERNEL_FROM and cache.head_dim % 16 == 0 and rank % 16 == 0 and rank <= 256):
+        # prompt portions: four tokens of a request share the cached blocks they read
+        _check(lib().llm_latent_attention_rows(
+            q_full.data_ptr(), out.data_ptr(), cache.k_ptr, cache.block_table.data_ptr(), cache.page_stride,
+            cache.table_stride, cache.page_tokens, cache.head_dim, rank, _ptr(sink), ctx.positions.data_ptr(),
+            ctx.seq_q_start.data_ptr(), ctx.seq_q_len.data_ptr(), ctx.row_seq.data_ptr(), heads, ctx.n_seqs,
+            ctx.max_q_len, float(scale), int(window), ctx.stream), "latent_attention_rows")
+        return
     if ctx.use_fast_attention and mma_takes(q_full.dtype, cache.head_dim, rank) and cache.dtype == torch.bfloat16:
         splits = key_splits(ctx.n_tokens, heads)
         floats = int(lib().llm_latent_attention_mma_scratch(ctx.n_tokens, heads, rank, splits))

@@ -62,18 +62,20 @@ def _stretch_scratch(device, floats: int) -> torch.Tensor:
     return buf
 
 
-def scan(ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, per_channel: bool,
+def scan(ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, per_channel,
          state: torch.Tensor, out: torch.Tensor, heads: int, dk: int, dv: int, q_scale: float = 1.0) -> None:
     """For every sequence of the step, in token order: S = diag(a) S + k v^T, o = S^T (q * q_scale),
     with S in `state[slot]` ([heads, dk, dv] float32) read at the start and written at the end.
     q, k [rows, heads * dk] and v [rows, heads * dv] may be column views of a wider matrix;
-    `decay` is [heads] or, with `per_channel`, [rows, heads * dk] float32.  out [rows, heads * dv]
+    `decay` is [heads] or, with `per_channel`, [rows, heads * dk] float32, or, with `per_channel`
+    == "token", one number per token and head, [rows, heads].  out [rows, heads * dv]
     float32.  A long portion of a bfloat16 step is walked as stretches of `STRETCH` tokens side by
     side, each from an empty state, and joined afterwards (two more kernels)."""
     _dev(q, k, v, decay, state, out)
     if not (q.dtype == k.dtype == v.dtype) or state.dtype != torch.float32 or out.dtype != torch.float32 \
             or decay.dtype != torch.float32 or not out.is_contiguous() or not decay.is_contiguous():
         raise KernelLaunchError("linear_attention_scan: element types or layout not as the kernel needs")
+    mode = 2 if per_channel == "token" else (1 if per_channel else 0)
     n_segs = _stretches(ctx, q, heads, dk, dv)
     seg_state = seg_decay = cum = 0
     if n_segs > 1:
@@ -84,7 +86,7 @@ def scan(ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Te
             cum = ctx.ws.get("scan_cum", (q.shape[0], heads * dk), torch.float32).data_ptr()
     _check(lib().llm_linear_attention_scan(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), dtype_code(q.dtype), q.stride(0), k.stride(0), v.stride(0),
-        decay.data_ptr(), 1 if per_channel else 0, state.data_ptr(), out.data_ptr(),
+        decay.data_ptr(), mode, state.data_ptr(), out.data_ptr(),
         ctx.seq_slot.data_ptr(), ctx.seq_q_start.data_ptr(), ctx.seq_q_len.data_ptr(), ctx.n_seqs, heads, dk, dv,
         float(q_scale), STRETCH, n_segs, seg_state, seg_decay, cum, ctx.stream), "linear_attention_scan")
     if n_segs > 1:

@@ -86,10 +86,10 @@ class MLSTM(Part):
         MK.gates(ctx, z, 0, H, self.i_bias, self.f_bias, self.cap, call.states[1], coef, H)
         qf = ctx.ws.get("mlstm_q", (n, kd), torch.float32)
         kf = ctx.ws.get("mlstm_k", (n, kd), torch.float32)
-        decay = ctx.ws.get("mlstm_decay", (n, kd), torch.float32)
+        decay = ctx.ws.get("mlstm_decay", (n, H), torch.float32)
         vf = ctx.ws.get("mlstm_v", (n, H * dvp), torch.float32)
         MK.operands(ctx, u, 0, kd, 2 * kd, coef, qf, kf, decay, vf, H, dk, dv, dvp)
         scanned = ctx.ws.get("mlstm_scan", (n, H * dvp), torch.float32)
-        LA.scan(ctx, qf, kf, vf, decay, True, call.states[0], scanned, H, dk, dvp, dk ** -0.5)
+        LA.scan(ctx, qf, kf, vf, decay, "token", call.states[0], scanned, H, dk, dvp, dk ** -0.5)
         MK.finish(ctx, scanned, coef, self.norm_w, u[:, 2 * kd + vd:], out, H, dv, dvp, self.eps)
         return self.o.forward(ctx, out, n, torch.float32, "mixer_out", allow_partials=True)

@@ -6,7 +6,7 @@
 // rotate turns the first `rot_dims` entries of a head pair by pair, entry 2i with entry 2i + 1, by
 // the angle position * inv_freq[i], cos and sin multiplied by `mag`; the other entries pass.  q goes
 // to its buffer, k into the request's cache page, and the values - a projection of their own, or
-// the keys as projected, before norm and rotation - beside it.  Norm, angle and rotation are float32.
+// the keys as projected, before norm and rotation - beside it.  Grid (token, share of the token's heads).  Norm, angle and rotation are float32.
 // Also here: the sigmoid gate on a mixer's output.
 
 #include "common.cuh"
@@ -30,7 +30,7 @@ headnorm_rope_cache_kernel(const T* __restrict__ u, long long u_stride, int q_co
   float* s = head_smem + warp * d;
   const int pos = positions[t], seq = row_seq[t];
   const T* row = u + (long long)t * u_stride;
-  for (int item = warp; item < q_heads + cache.kv_heads; item += PREP_WARPS) {
+  for (int item = blockIdx.y * PREP_WARPS + warp; item < q_heads + cache.kv_heads; item += gridDim.y * PREP_WARPS) {
     const bool is_q = item < q_heads;
     const int h = is_q ? item : item - q_heads;
     const T* x = row + (is_q ? q_col : k_col) + h * d;
@@ -86,12 +86,15 @@ extern "C" int llm_headnorm_rope_cache(const void* u, int dtype, long long u_str
   const size_t smem = (size_t)PREP_WARPS * head_dim * sizeof(float);
   LLM_HOST_CHECK(smem <= 48 * 1024, ERR_BAD_SIZE);
   PagedCache c{k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads, head_dim};
+  // few tokens: a token's heads are dealt to several blocks, so that the step still fills the GPU
+  const int per_token = n_tokens >= 256 ? 1 : min((q_heads + kv_heads + PREP_WARPS - 1) / PREP_WARPS, 16);
+  const dim3 grid(n_tokens, per_token);
   if (dtype == DT_F32)
-    launch_kernel(headnorm_rope_cache_kernel<float, float>, n_tokens, PREP_WARPS * 32, smem, stream, (const float*)u,
+    launch_kernel(headnorm_rope_cache_kernel<float, float>, grid, PREP_WARPS * 32, smem, stream, (const float*)u,
                   u_stride, q_col, k_col, v_col, (const float*)q_norm_w, (const float*)k_norm_w, eps, inv_freq, rot_dims,
                   mag, (float*)q_out, c, v_dim, positions, row_seq, q_heads, write_cache);
   else if (dtype == DT_BF16)
-    launch_kernel(headnorm_rope_cache_kernel<__nv_bfloat16, __nv_bfloat16>, n_tokens, PREP_WARPS * 32, smem, stream,
+    launch_kernel(headnorm_rope_cache_kernel<__nv_bfloat16, __nv_bfloat16>, grid, PREP_WARPS * 32, smem, stream,
                   (const __nv_bfloat16*)u, u_stride, q_col, k_col, v_col, (const __nv_bfloat16*)q_norm_w,
                   (const __nv_bfloat16*)k_norm_w, eps, inv_freq, rot_dims, mag, (__nv_bfloat16*)q_out, c, v_dim,
                   positions, row_seq, q_heads, write_cache);

@@ -172,10 +172,97 @@ per_head_linear_kernel(const T* __restrict__ x, long long x_row, long long x_hea
   }
 }
 
+// The same for a step of few tokens (decoding), where a 64 x 64 tile would leave one thread block per
+// head: grid (head, 64 outputs).  The head's inputs of all tokens wait in shared memory as float32.
+// W_IN_ROWS: a thread takes one output (neighbouring threads neighbouring outputs of a weight row) and
+// a quarter of the inputs, the quarters meet in shared memory; else a warp takes 8 outputs in turn, its
+// lanes stride over a weight row's inputs.  Sums are float32.
+#define PHF_TOKENS 16
+
+template <typename T, bool W_IN_ROWS>
+__global__ void __launch_bounds__(256)
+per_head_linear_few_kernel(const T* __restrict__ x, long long x_row, long long x_head, const T* __restrict__ w,
+                           T* __restrict__ out, long long o_row, long long o_head, const T* __restrict__ gate,
+                           long long gate_row, int n_tokens, int n_in, int n_out) {
+  pdl_launch_dependents();
+  extern __shared__ float phf_smem[];      // x [n_tokens][n_in], then partial sums [4][PHF_TOKENS][64]
+  float* xs = phf_smem;
+  float* parts = phf_smem + n_tokens * n_in;
+  const int h = blockIdx.x, o0 = blockIdx.y * 64;
+  const T* wh = w + (long long)h * n_in * n_out;
+  pdl_wait();
+  for (int e = threadIdx.x; e < n_tokens * n_in; e += 256) {
+    const int t = e / n_in, i = e - t * n_in;
+    xs[e] = to_float(x[(long long)t * x_row + (long long)h * x_head + i]);
+  }
+  __syncthreads();
+  float acc[PHF_TOKENS];
+#pragma unroll
+  for (int t = 0; t < PHF_TOKENS; ++t) acc[t] = 0.0f;
+  if (W_IN_ROWS) {
+    const int oo = threadIdx.x & 63, part = threadIdx.x >> 6, o = o0 + oo;
+    const int per = (n_in + 3) / 4, i0 = part * per, i1 = min(n_in, i0 + per);
+    if (o < n_out)
+      for (int i = i0; i < i1; ++i) {
+        const float wv = to_float(wh[(long long)i * n_out + o]);
+#pragma unroll
+        for (int t = 0; t < PHF_TOKENS; ++t)
+          if (t < n_tokens) acc[t] = fmaf(xs[t * n_in + i], wv, acc[t]);
+      }
+#pragma unroll
+    for (int t = 0; t < PHF_TOKENS; ++t)
+      if (t < n_tokens) parts[(part * PHF_TOKENS + t) * 64 + oo] = acc[t];
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_tokens * 64; e += 256) {
+      const int t = e >> 6, c = e & 63, oc = o0 + c;
+      if (oc >= n_out) continue;
+      float v = (parts[(0 * PHF_TOKENS + t) * 64 + c] + parts[(1 * PHF_TOKENS + t) * 64 + c]) +
+                (parts[(2 * PHF_TOKENS + t) * 64 + c] + parts[(3 * PHF_TOKENS + t) * 64 + c]);
+      if (gate) v = v / (1.0f + expf(-to_float(gate[(long long)t * gate_row + (long long)h * n_out + oc])));
+      out[(long long)t * o_row + (long long)h * o_head + oc] = from_float<T>(v);
+    }
+  } else {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int j = 0; j < 8; ++j) {
+      const int o = o0 + warp * 8 + j;
+      if (o >= n_out) break;
+#pragma unroll
+      for (int t = 0; t < PHF_TOKENS; ++t) acc[t] = 0.0f;
+      for (int i = lane; i < n_in; i += 32) {
+        const float wv = to_float(wh[(long long)o * n_in + i]);
+#pragma unroll
+        for (int t = 0; t < PHF_TOKENS; ++t)
+          if (t < n_tokens) acc[t] = fmaf(xs[t * n_in + i], wv, acc[t]);
+      }
+#pragma unroll
+      for (int t = 0; t < PHF_TOKENS; ++t)
+        if (t < n_tokens) {
+          float v = warp_sum(acc[t]);
+          if (lane == 0) {
+            if (gate) v = v / (1.0f + expf(-to_float(gate[(long long)t * gate_row + (long long)h * n_out + o])));
+            out[(long long)t * o_row + (long long)h * o_head + o] = from_float<T>(v);
+          }
+        }
+    }
+  }
+}
+
 extern "C" int llm_per_head_linear(const void* x, long long x_row, long long x_head, const void* w, int w_in_rows,
                                    void* out, long long o_row, long long o_head, const void* gate, long long gate_row,
                                    int dtype, int n_tokens, int heads, int n_in, int n_out, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  const size_t few_smem = ((size_t)n_tokens * n_in + 4 * PHF_TOKENS * 64) * sizeof(float);
+  if (n_tokens <= PHF_TOKENS && few_smem <= 48 * 1024 && (n_out + 63) / 64 <= 65535) {
+    dim3 few_grid(heads, (n_out + 63) / 64);
+#define FEW(T, IN_ROWS)                                                                                               \
+  launch_kernel(per_head_linear_few_kernel<T, IN_ROWS>, few_grid, 256, few_smem, stream, (const T*)x, x_row, x_head, \
+                (const T*)w, (T*)out, o_row, o_head, (const T*)gate, gate_row, n_tokens, n_in, n_out)
+    if (dtype == DT_F32) { if (w_in_rows) FEW(float, true); else FEW(float, false); }
+    else if (dtype == DT_BF16) { if (w_in_rows) FEW(__nv_bfloat16, true); else FEW(__nv_bfloat16, false); }
+    else return ERR_BAD_DTYPE;
+#undef FEW
+    return launch_status();
+  }
   dim3 grid((n_tokens + PH_TILE - 1) / PH_TILE, (n_out + PH_TILE - 1) / PH_TILE, heads);
   LLM_HOST_CHECK(grid.y <= 65535 && grid.z <= 65535, ERR_BAD_SIZE);
 #define GO(T, IN_ROWS)                                                                                             \
@@ -569,32 +656,35 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
 }
 
 // One block per (tile, row): the splits' (O, max, sum) and the sink -> the row's weighted latent.
+// The splits' weights 2^(max_s - max) / sum are worked out once, in shared memory.
 __global__ void __launch_bounds__(128)
 latent_attention_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                               const __nv_bfloat16* __restrict__ sink, int heads, int head_groups, int rank,
                               int n_splits) {
   pdl_launch_dependents();
   pdl_wait();
+  __shared__ float wt[64], red[2];      // n_splits <= 32 (two entries per split while they are reduced)
   const int tile = blockIdx.x >> 4, r = blockIdx.x & 15;
   const int t = tile / head_groups, h = (tile - t * head_groups) * 16 + r;
   if (h >= heads) return;
   const float* base = partial + ((long long)tile * n_splits * 16 + r) * (rank + 2);
   const long long step = (long long)16 * (rank + 2);
-  float top = sink ? __bfloat162float(sink[h]) * 1.4426950408889634f : -INFINITY;
-  const float sk = top;
-  for (int s = 0; s < n_splits; ++s) top = fmaxf(top, base[s * step + rank]);
-  float total = sink ? exp2f(sk - top) : 0.0f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float m = base[s * step + rank];
-    if (m != -INFINITY) total += base[s * step + rank + 1] * exp2f(m - top);
+  if (threadIdx.x < 32) {
+    const int s = threadIdx.x;
+    const float m = s < n_splits ? base[s * step + rank] : -INFINITY;
+    const float l = s < n_splits ? base[s * step + rank + 1] : 0.0f;
+    const float sk = sink ? __bfloat162float(sink[h]) * 1.4426950408889634f : -INFINITY;
+    const float top = fmaxf(warp_max(m), sk);
+    const float wgt = m == -INFINITY ? 0.0f : exp2f(m - top);
+    const float total = warp_sum(l * wgt) + (sink ? exp2f(sk - top) : 0.0f);
+    wt[s] = wgt;
+    if (s == 0) red[0] = total > 0.0f ? 1.0f / total : 0.0f;
   }
-  const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+  __syncthreads();
+  const float inv = red[0];
   for (int c = threadIdx.x; c < rank; c += blockDim.x) {
     float acc = 0.0f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float m = base[s * step + rank];
-      if (m != -INFINITY) acc += base[s * step + c] * exp2f(m - top);
-    }
+    for (int s = 0; s < n_splits; ++s) acc = fmaf(base[s * step + c], wt[s], acc);
     out[((long long)t * heads + h) * rank + c] = __float2bfloat16_rn(acc * inv);
   }
 }
@@ -824,7 +914,7 @@ extern "C" int llm_latent_attention_mma(const void* q, void* out, float* partial
                                         int n_splits, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   LLM_HOST_CHECK(D % 16 == 0 && rank % 32 == 0 && rank >= 32 && rank <= 32 * LM_MAX_NT && rank <= D, ERR_BAD_SIZE);
-  LLM_HOST_CHECK(n_splits >= 1 && n_splits <= 65535 && (n_splits == 1 || partial), ERR_BAD_SIZE);
+  LLM_HOST_CHECK(n_splits >= 1 && n_splits <= 32 && (n_splits == 1 || partial), ERR_BAD_SIZE);
   LLM_HOST_CHECK(((uintptr_t)q % 16) == 0 && ((uintptr_t)k_base % 16) == 0 && page_stride % 8 == 0, ERR_BAD_ALIGN);
   PagedCache c{k_base, k_base, block_table, page_stride, table_stride, page_tokens, 1, D};
   const int head_groups = (heads + 15) / 16;

@@ -232,15 +232,29 @@ mlstm_step_kernel(const T* __restrict__ u, long long u_stride, int q_col, int k_
   float acc[STEP_MAX_COLS];
 #pragma unroll
   for (int j = 0; j < STEP_MAX_COLS; ++j) acc[j] = 0.0f;
-  for (int r = warp; r < dk; r += 8) {
-    const float kr = kk[r], qr = qs[r];
+  // four rows at a time: their loads are under way together
+  for (int r = warp; r < dk; r += 32) {
+    float sv[4][STEP_MAX_COLS];
 #pragma unroll
-    for (int j = 0; j < STEP_MAX_COLS; ++j) {
-      const int c = lane + 32 * j;
-      if (c < dvp) {
-        const float v = a * S[(long long)r * dvp + c] + kr * vs[c];
-        S[(long long)r * dvp + c] = v;
-        acc[j] = fmaf(v, qr, acc[j]);
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < STEP_MAX_COLS; ++j) {
+        const int c = lane + 32 * j, rr = r + 8 * i;
+        if (c < dvp && rr < dk) sv[i][j] = S[(long long)rr * dvp + c];
+      }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int rr = r + 8 * i;
+      if (rr >= dk) break;
+      const float kr = kk[rr], qr = qs[rr];
+#pragma unroll
+      for (int j = 0; j < STEP_MAX_COLS; ++j) {
+        const int c = lane + 32 * j;
+        if (c < dvp) {
+          const float v = a * sv[i][j] + kr * vs[c];
+          S[(long long)rr * dvp + c] = v;
+          acc[j] = fmaf(v, qr, acc[j]);
+        }
       }
     }
   }

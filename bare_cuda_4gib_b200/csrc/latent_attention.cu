@@ -173,10 +173,10 @@ per_head_linear_kernel(const T* __restrict__ x, long long x_row, long long x_hea
 }
 
 // The same for a step of few tokens (decoding), where a 64 x 64 tile would leave one thread block per
-// head: grid (head, 64 outputs).  The head's inputs of all tokens wait in shared memory as float32.
-// W_IN_ROWS: a thread takes one output (neighbouring threads neighbouring outputs of a weight row) and
-// a quarter of the inputs, the quarters meet in shared memory; else a warp takes 8 outputs in turn, its
-// lanes stride over a weight row's inputs.  Sums are float32.
+// head.  The head's inputs of all tokens wait in shared memory as float32.  W_IN_ROWS: grid (head, 64
+// outputs); a thread takes one output (neighbouring threads neighbouring outputs of a weight row) and
+// a quarter of the inputs, the quarters meet in shared memory.  Else: grid (head, 8 outputs); a warp
+// takes one output, its lanes stride over the weight row's inputs.  Sums are float32.
 #define PHF_TOKENS 16
 
 template <typename T, bool W_IN_ROWS>
@@ -188,7 +188,7 @@ per_head_linear_few_kernel(const T* __restrict__ x, long long x_row, long long x
   extern __shared__ float phf_smem[];      // x [n_tokens][n_in], then partial sums [4][PHF_TOKENS][64]
   float* xs = phf_smem;
   float* parts = phf_smem + n_tokens * n_in;
-  const int h = blockIdx.x, o0 = blockIdx.y * 64;
+  const int h = blockIdx.x, o0 = blockIdx.y * (W_IN_ROWS ? 64 : 8);
   const T* wh = w + (long long)h * n_in * n_out;
   pdl_wait();
   for (int e = threadIdx.x; e < n_tokens * n_in; e += 256) {
@@ -223,11 +223,8 @@ per_head_linear_few_kernel(const T* __restrict__ x, long long x_row, long long x
     }
   } else {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int j = 0; j < 8; ++j) {
-      const int o = o0 + warp * 8 + j;
-      if (o >= n_out) break;
-#pragma unroll
-      for (int t = 0; t < PHF_TOKENS; ++t) acc[t] = 0.0f;
+    const int o = o0 + warp;
+    if (o < n_out) {
       for (int i = lane; i < n_in; i += 32) {
         const float wv = to_float(wh[(long long)o * n_in + i]);
 #pragma unroll
@@ -238,7 +235,7 @@ per_head_linear_few_kernel(const T* __restrict__ x, long long x_row, long long x
       for (int t = 0; t < PHF_TOKENS; ++t)
         if (t < n_tokens) {
           float v = warp_sum(acc[t]);
-          if (lane == 0) {
+          if (lane == (t & 31)) {
             if (gate) v = v / (1.0f + expf(-to_float(gate[(long long)t * gate_row + (long long)h * n_out + o])));
             out[(long long)t * o_row + (long long)h * o_head + o] = from_float<T>(v);
           }
@@ -252,8 +249,8 @@ extern "C" int llm_per_head_linear(const void* x, long long x_row, long long x_h
                                    int dtype, int n_tokens, int heads, int n_in, int n_out, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const size_t few_smem = ((size_t)n_tokens * n_in + 4 * PHF_TOKENS * 64) * sizeof(float);
-  if (n_tokens <= PHF_TOKENS && few_smem <= 48 * 1024 && (n_out + 63) / 64 <= 65535) {
-    dim3 few_grid(heads, (n_out + 63) / 64);
+  if (n_tokens <= PHF_TOKENS && few_smem <= 48 * 1024 && (n_out + 7) / 8 <= 65535) {
+    dim3 few_grid(heads, w_in_rows ? (n_out + 63) / 64 : (n_out + 7) / 8);
 #define FEW(T, IN_ROWS)                                                                                               \
   launch_kernel(per_head_linear_few_kernel<T, IN_ROWS>, few_grid, 256, few_smem, stream, (const T*)x, x_row, x_head, \
                 (const T*)w, (T*)out, o_row, o_head, (const T*)gate, gate_row, n_tokens, n_in, n_out)

@@ -244,6 +244,12 @@ per_head_linear_few_kernel(const T* __restrict__ x, long long x_row, long long x
   }
 }
 
+static int per_head_linear_mma(const void* x, long long x_row, long long x_head, const void* w, int w_in_rows, void* out,
+                               long long o_row, long long o_head, const void* gate, long long gate_row, int n_tokens,
+                               int heads, int n_in, int n_out, cudaStream_t stream);
+static bool per_head_mma_takes(const void* x, long long x_row, long long x_head, const void* w, int w_in_rows, int n_in,
+                               int n_out);
+
 extern "C" int llm_per_head_linear(const void* x, long long x_row, long long x_head, const void* w, int w_in_rows,
                                    void* out, long long o_row, long long o_head, const void* gate, long long gate_row,
                                    int dtype, int n_tokens, int heads, int n_in, int n_out, cudaStream_t stream) {
@@ -262,6 +268,9 @@ extern "C" int llm_per_head_linear(const void* x, long long x_row, long long x_h
   }
   dim3 grid((n_tokens + PH_TILE - 1) / PH_TILE, (n_out + PH_TILE - 1) / PH_TILE, heads);
   LLM_HOST_CHECK(grid.y <= 65535 && grid.z <= 65535, ERR_BAD_SIZE);
+  if (dtype == DT_BF16 && per_head_mma_takes(x, x_row, x_head, w, w_in_rows, n_in, n_out))
+    return per_head_linear_mma(x, x_row, x_head, w, w_in_rows, out, o_row, o_head, gate, gate_row, n_tokens, heads, n_in,
+                               n_out, stream);
 #define GO(T, IN_ROWS)                                                                                             \
   launch_kernel(per_head_linear_kernel<T, IN_ROWS>, grid, 256, 0, stream, (const T*)x, x_row, x_head, (const T*)w, \
                 (T*)out, o_row, o_head, (const T*)gate, gate_row, n_tokens, n_in, n_out)
@@ -896,6 +905,103 @@ extern "C" int llm_latent_attention_rows(const void* q, void* out, void* k_base,
   else if (rank <= 128) GO(16);
   else GO(32);
 #undef GO
+  return launch_status();
+}
+
+// One matrix per head on mma.sync, for bfloat16 steps of many tokens whose rows are 16-byte aligned:
+// a block takes 64 tokens x 64 outputs of one head, a warp 16 tokens; inputs and the head's weights
+// arrive 32 inputs at a time by asynchronous copies, two stages deep; float32 sums.
+template <bool W_IN_ROWS>
+__global__ void __launch_bounds__(128)
+per_head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_row, long long x_head,
+                           const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long o_row,
+                           long long o_head, const __nv_bfloat16* __restrict__ gate, long long gate_row, int n_tokens,
+                           int n_in, int n_out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int XLD = 40, WLD = W_IN_ROWS ? 72 : 40, WROWS = W_IN_ROWS ? 32 : 64;
+  __shared__ __align__(16) __nv_bfloat16 xs[2][64 * XLD];
+  __shared__ __align__(16) __nv_bfloat16 ws[2][WROWS * WLD];
+  const int h = blockIdx.z, t0 = blockIdx.x * 64, o0 = blockIdx.y * 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const __nv_bfloat16* wh = w + (long long)h * n_in * n_out;
+  auto copies = [&](int k0, int stage) {
+    for (int e = threadIdx.x; e < 64 * 4; e += 128) {          // x: 64 tokens x 4 pieces of 8 inputs
+      const int r = e >> 2, c = (e & 3) * 8, t = t0 + r, k = k0 + c;
+      const bool valid = t < n_tokens && k < n_in;
+      cp_async_16_or_zero(&xs[stage][r * XLD + c], x + (valid ? (long long)t * x_row + (long long)h * x_head + k : 0), valid);
+    }
+    if (W_IN_ROWS) {                                           // w: 32 inputs x 8 pieces of 8 outputs
+      for (int e = threadIdx.x; e < 32 * 8; e += 128) {
+        const int r = e >> 3, c = (e & 7) * 8, k = k0 + r, o = o0 + c;
+        const bool valid = k < n_in && o < n_out;
+        cp_async_16_or_zero(&ws[stage][r * WLD + c], wh + (valid ? (long long)k * n_out + o : 0), valid);
+      }
+    } else {                                                   // w: 64 outputs x 4 pieces of 8 inputs
+      for (int e = threadIdx.x; e < 64 * 4; e += 128) {
+        const int r = e >> 2, c = (e & 3) * 8, o = o0 + r, k = k0 + c;
+        const bool valid = o < n_out && k < n_in;
+        cp_async_16_or_zero(&ws[stage][r * WLD + c], wh + (valid ? (long long)o * n_in + k : 0), valid);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+  copies(0, 0);
+  int stage = 0;
+  for (int k0 = 0; k0 < n_in; k0 += 32, stage ^= 1) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                      // this stage has arrived, the other one has been read
+    if (k0 + 32 < n_in) copies(k0 + 32, stage ^ 1);
+#pragma unroll
+    for (int kk = 0; kk < 32; kk += 16) {
+      uint32_t a[4];
+      ldsm_x4(a, &xs[stage][(warp * 16 + (lane & 15)) * XLD + kk + (lane >> 4) * 8]);
+#pragma unroll
+      for (int i = 0; i < 8; i += 2) {
+        uint32_t b[4];
+        if (W_IN_ROWS)
+          ldsm_x4_trans(b, &ws[stage][(kk + (lane & 7) + ((lane >> 3) & 1) * 8) * WLD + i * 8 + ((lane >> 4) & 1) * 8]);
+        else
+          ldsm_x4(b, &ws[stage][(i * 8 + (lane & 7) + ((lane >> 4) & 1) * 8) * WLD + kk + ((lane >> 3) & 1) * 8]);
+        mma_bf16(acc[i], a, b[0], b[1]);
+        mma_bf16(acc[i + 1], a, b[2], b[3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int t = t0 + warp * 16 + (lane >> 2) + (e >= 2 ? 8 : 0), o = o0 + i * 8 + (lane & 3) * 2 + (e & 1);
+      if (t >= n_tokens || o >= n_out) continue;
+      float v = acc[i][e];
+      if (gate) v = v / (1.0f + expf(-__bfloat162float(gate[(long long)t * gate_row + (long long)h * n_out + o])));
+      out[(long long)t * o_row + (long long)h * o_head + o] = __float2bfloat16_rn(v);
+    }
+}
+
+// Whether the mma.sync form can read these operands with 16-byte copies.
+static bool per_head_mma_takes(const void* x, long long x_row, long long x_head, const void* w, int w_in_rows, int n_in,
+                               int n_out) {
+  return ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 && x_row % 8 == 0 && x_head % 8 == 0 && n_in % 8 == 0 &&
+         (w_in_rows ? n_out % 8 == 0 : true);
+}
+
+static int per_head_linear_mma(const void* x, long long x_row, long long x_head, const void* w, int w_in_rows, void* out,
+                               long long o_row, long long o_head, const void* gate, long long gate_row, int n_tokens,
+                               int heads, int n_in, int n_out, cudaStream_t stream) {
+  dim3 grid((n_tokens + 63) / 64, (n_out + 63) / 64, heads);
+  if (w_in_rows)
+    launch_kernel(per_head_linear_mma_kernel<true>, grid, 128, 0, stream, (const __nv_bfloat16*)x, x_row, x_head,
+                  (const __nv_bfloat16*)w, (__nv_bfloat16*)out, o_row, o_head, (const __nv_bfloat16*)gate, gate_row,
+                  n_tokens, n_in, n_out);
+  else
+    launch_kernel(per_head_linear_mma_kernel<false>, grid, 128, 0, stream, (const __nv_bfloat16*)x, x_row, x_head,
+                  (const __nv_bfloat16*)w, (__nv_bfloat16*)out, o_row, o_head, (const __nv_bfloat16*)gate, gate_row,
+                  n_tokens, n_in, n_out);
   return launch_status();
 }
 

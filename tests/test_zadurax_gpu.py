@@ -94,8 +94,10 @@ def test_norm_kernels():
     assert H.row_error(emb, P.rms_norm(table[[3, 29, 0, 3]], wn, 1e-5)) < 1e-6
 
 
+@pytest.mark.parametrize("n,n_in,n_out,spare", [(70, 19, 66, 5), (150, 24, 72, 8), (9, 40, 13, 0), (200, 64, 8, 0)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_one_matrix_per_head(dtype):
+def test_one_matrix_per_head(dtype, n, n_in, n_out, spare):
+    """Rows that are and are not 16-byte aligned, few and many tokens: every kernel of the product."""
     from bare_cuda_4gib_b200.kernels import latent as LT
 
     class Ctx:
@@ -103,8 +105,8 @@ def test_one_matrix_per_head(dtype):
 
     Ctx.stream = torch.cuda.current_stream().cuda_stream
     g = torch.Generator().manual_seed(8)
-    n, heads, n_in, n_out = 70, 3, 19, 66
-    x = torch.randn(n, heads, n_in + 5, generator=g).to(dtype).cuda()          # rows wider than what is read
+    heads = 3
+    x = torch.randn(n, heads, n_in + spare, generator=g).to(dtype).cuda()      # rows wider than what is read
     w_rows = torch.randn(heads * n_in, n_out, generator=g).to(dtype).cuda()
     w_cols = torch.randn(heads * n_out, n_in, generator=g).to(dtype).cuda()
     gate = torch.randn(n, heads * n_out, generator=g).to(dtype).cuda()

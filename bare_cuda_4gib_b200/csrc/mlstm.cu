@@ -21,7 +21,7 @@
 
 // Grid (sequence, head).  coef[row][head] = (a, b, exp(-m), m) for every new token of the sequence;
 // m_state[slot][head] is read at the start and written at the end.  The gates of a chunk of tokens
-// are computed side by side, one thread walks m through the chunk, then a and b side by side.
+// are computed side by side, m is walked through the chunk as a scan, then a and b side by side.
 template <typename TW>
 __global__ void __launch_bounds__(GATE_THREADS)
 mlstm_gates_kernel(const float* __restrict__ z, long long z_stride, int i_col, int f_col, const TW* __restrict__ i_bias,
@@ -30,7 +30,7 @@ mlstm_gates_kernel(const float* __restrict__ z, long long z_stride, int i_col, i
                    const int32_t* __restrict__ seq_q_len, int heads) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float gi[GATE_CHUNK], gf[GATE_CHUNK], mm[GATE_CHUNK + 1];
+  __shared__ float gi[GATE_CHUNK], gf[GATE_CHUNK], mm[GATE_CHUNK + 1], wF[GATE_THREADS / 32], wI[GATE_THREADS / 32];
   const int s = blockIdx.x, h = blockIdx.y;
   const int len = seq_q_len[s];
   if (len <= 0) return;
@@ -47,13 +47,49 @@ mlstm_gates_kernel(const float* __restrict__ z, long long z_stride, int i_col, i
       gf[t] = fminf(u, 0.0f) - log1pf(expf(-fabsf(u)));      // logsigmoid(u)
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      float m = m_prev;
-      mm[0] = m;
-      for (int t = 0; t < n; ++t) {
-        m = fmaxf(gf[t] + m, gi[t]);
-        mm[t + 1] = m;
+    // A token maps m to max(m + f, i); two tokens in a row map it to max(m + (f1 + f2), max(i1 + f2, i2)).
+    // So a thread folds the maps of its four tokens, the threads' maps are scanned (shuffles inside a
+    // warp, the warps' totals through shared memory), and every thread walks its four tokens from the
+    // m that comes in.
+    {
+      const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, t0 = threadIdx.x * 4;
+      float F = 0.0f, I = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (t0 + j < n) {
+          F += gf[t0 + j];
+          I = fmaxf(I + gf[t0 + j], gi[t0 + j]);
+        }
+      for (int o = 1; o < 32; o <<= 1) {
+        const float pF = __shfl_up_sync(0xffffffffu, F, o), pI = __shfl_up_sync(0xffffffffu, I, o);
+        if (lane >= o) {
+          I = fmaxf(pI + F, I);      // the earlier map first, then this one
+          F = pF + F;
+        }
       }
+      if (lane == 31) {
+        wF[warp] = F;
+        wI[warp] = I;
+      }
+      float eF = __shfl_up_sync(0xffffffffu, F, 1), eI = __shfl_up_sync(0xffffffffu, I, 1);
+      if (lane == 0) {
+        eF = 0.0f;
+        eI = -INFINITY;
+      }
+      __syncthreads();
+      float pF = 0.0f, pI = -INFINITY;
+      for (int v = 0; v < warp; ++v) {
+        pI = fmaxf(pI + wF[v], wI[v]);
+        pF += wF[v];
+      }
+      float m = fmaxf(m_prev + (pF + eF), fmaxf(pI + eF, eI));
+      if (threadIdx.x == 0) mm[0] = m_prev;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (t0 + j < n) {
+          m = fmaxf(gf[t0 + j] + m, gi[t0 + j]);
+          mm[t0 + j + 1] = m;
+        }
     }
     __syncthreads();
     for (int t = threadIdx.x; t < n; t += blockDim.x) {

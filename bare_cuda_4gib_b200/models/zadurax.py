@@ -57,11 +57,9 @@ def zadurax_spec(cfg: ZaduraxConfig) -> ModelSpec:
     def norm(name):
         return PartSpec("sandwich_rmsnorm", {"size": cfg.width, "eps": cfg.norm_eps}, {"weight": name})
 
-    layers, own, order = [], {}, []
+    layers, own = [], {}
     for i, layer in enumerate(cfg.layers):
-        src = layer.get("weights_of")
-        if src is not None:
-            order.append(LayerCall(own[src]))
+        if layer.get("weights_of") is not None:
             continue
         name = f"l{i}"
         mlp = layer.get("mlp")
@@ -69,7 +67,6 @@ def zadurax_spec(cfg: ZaduraxConfig) -> ModelSpec:
         if mlp is not None:
             extras["post2"] = norm(name + ".norm2b")
         own[i] = len(layers)
-        order.append(LayerCall(own[i]))
         layers.append(LayerSpec(
             mixer_norm=norm(name + ".norm1"),
             mixer=_MIXERS[layer["type"]](cfg, layer["mixer"], name + ".mix."),
@@ -78,6 +75,10 @@ def zadurax_spec(cfg: ZaduraxConfig) -> ModelSpec:
                          {"gate": name + ".mlp.gate", "up": name + ".mlp.up", "down": name + ".mlp.down"})
             if mlp is not None else None,
             block="sandwich", extras=extras))
+    # the run order follows the configuration; a layer without tensors of its own is one more run of the
+    # layer it names (which may stand before or behind it)
+    order = [LayerCall(own[i if layer.get("weights_of") is None else layer["weights_of"]])
+             for i, layer in enumerate(cfg.layers)]
     sizes = {"vocab": cfg.vocab, "hidden": cfg.width}
     return ModelSpec(
         architecture=ZaduraxConfig.ARCHITECTURE, hidden_size=cfg.width, vocab_size=cfg.vocab, max_positions=None,

@@ -49,6 +49,15 @@ def test_layers_that_share_tensors_run_again_with_a_cache_of_their_own():
     assert len(cache.states) == 4
 
 
+def test_a_layer_may_use_the_tensors_of_a_later_one():
+    layers = [Z.again([None, Z.mlstm(2, 8, 8, 5.0)], 1), Z.mlstm(2, 8, 8, 5.0), Z.attention(2, 1, 16, 9, 4, ff=24)]
+    cfg = {"architecture": "Zadurax", "vocab": 40, "width": 32, "norm": {"eps": 1e-6}, "layers": layers}
+    spec = _spec(cfg)
+    assert [c.layer for c in spec.order] == [0, 0, 1] and len(spec.layers) == 2
+    expected, _ = expected_weights(spec)
+    assert "l1.mix.q" in expected and "l2.mlp.gate" in expected and not any(k.startswith("l0.") for k in expected)
+
+
 def test_configuration_errors_name_the_key():
     def broken(change):
         cfg = copy.deepcopy(Z.CFG_P)

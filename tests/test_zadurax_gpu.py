@@ -47,6 +47,7 @@ ALONE = {
     "latent_tensor_cores": [Z.latent(5, 16, 16, 8, 32, 0.2, scaling=Z.yarn(4.0, 64, 16.0, 2.0))],
     "latent_two_tiles_of_heads": [Z.latent(18, 8, 32, 8, 96, 0.15, base=1000.0)],
     "latent_wide": [Z.latent(2, 8, 32, 8, 256, 0.1, scaling=Z.yarn(2.0, 32, 4.0, 1.0))],
+    "first_layer_uses_the_second_ones_tensors": [Z.again([None, Z.latent(2, 8, 8, 8, 16, 0.3)], 1), Z.latent(2, 8, 8, 8, 16, 0.3)],
     "mlstm": [Z.mlstm(3, 8, 20, 15.0)],
     "mlstm_one_head_tight_gates": [Z.mlstm(1, 40, 12, 1.5, ff=48)],
     "mlstm_wide": [Z.mlstm(2, 64, 64, 30.0)],

@@ -418,7 +418,7 @@ def _random_config(seed):
         rot = pick([2, 4, 8, 16, 32])
         scaling = pick([None, Z.yarn(pick([2.0, 8.0, 40.0]), pick([16, 64, 1000]), pick([4.0, 32.0]), pick([0.5, 1.0, 2.0]))])
         return Z.latent(pick([1, 2, 3, 5, 9, 17]), pick([4, 8, 12, 32, 64]), rot, pick([4, 8, 20, 64]), pick([8, 24, 32, 50, 64, 96]),
-                        pick([0.05, 0.125, 0.3]), base=pick([100.0, 50000.0]), scaling=scaling, ff=ff())
+                        pick([0.05, 0.11, 0.3]), base=pick([100.0, 30000.0]), scaling=scaling, ff=ff())
 
     def mlstm():
         return Z.mlstm(pick([1, 2, 3, 6]), pick([4, 8, 12, 16, 32, 40, 64]), pick([4, 8, 10, 16, 24, 64]),

@@ -29,13 +29,14 @@ __device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
                : "memory");
 }
 
-// ROWS numbers starting at p (16-byte aligned when VEC) as floats.
+// ROWS numbers as floats.  VEC: 16-byte pieces (8 bfloat16 or 4 float32 numbers each, 16-byte aligned),
+// piece j starting at p + j * stride; else the ROWS numbers starting at p.
 template <typename T, int ROWS, bool VEC>
-__device__ __forceinline__ void load_rows(const T* p, int valid, float (&dst)[ROWS]) {
+__device__ __forceinline__ void load_rows(const T* p, int valid, float (&dst)[ROWS], int stride) {
   if constexpr (VEC && sizeof(T) == 2) {
 #pragma unroll
     for (int j = 0; j < ROWS / 8; ++j) {
-      const uint4 raw = reinterpret_cast<const uint4*>(p)[j];
+      const uint4 raw = *reinterpret_cast<const uint4*>(p + j * stride);
       const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -46,7 +47,7 @@ __device__ __forceinline__ void load_rows(const T* p, int valid, float (&dst)[RO
   } else if constexpr (VEC) {
 #pragma unroll
     for (int j = 0; j < ROWS / 4; ++j) {
-      const float4 raw = reinterpret_cast<const float4*>(p)[j];
+      const float4 raw = *reinterpret_cast<const float4*>(p + j * stride);
       dst[j * 4] = raw.x; dst[j * 4 + 1] = raw.y; dst[j * 4 + 2] = raw.z; dst[j * 4 + 3] = raw.w;
     }
   } else {
@@ -56,10 +57,13 @@ __device__ __forceinline__ void load_rows(const T* p, int valid, float (&dst)[RO
 }
 
 // Grid (sequence, head, slice of value columns).  A warp's 32 lanes are `ks` row groups times
-// 32 / ks value columns; a thread owns the ROWS neighbouring state rows kr * ROWS .. of one column,
-// so a token costs it ROWS multiply-adds for the state, ROWS for the output, log2(ks) shuffles, and
-// (VEC: rows and buffers 16-byte aligned, every thread's rows inside the key size) a few 16-byte
-// loads of q and k from shared memory.
+// 32 / ks value columns; a thread owns ROWS state rows of one column, so a token costs it ROWS
+// multiply-adds for the state, ROWS for the output, log2(ks) shuffles, and (VEC: rows and buffers
+// 16-byte aligned, the threads' rows cover the key size exactly) a few 16-byte loads of q and k from
+// shared memory.  Which rows: without VEC the neighbouring rows kr * ROWS ..; with VEC 16-byte pieces
+// dealt round-robin to the row groups (piece j of group kr covers rows (j * ks + kr) * PIECE ..), so
+// that the row groups of a warp read neighbouring pieces of a token's q and k and no two of them
+// meet in a shared-memory bank.
 // Tokens come through shared memory a chunk at a time, SCAN_BUFFERS chunks deep: while the block walks
 // one chunk, the next ones' q, k, v (and decays) are on their way as 16-byte asynchronous copies, as
 // the projection left them (rows and head slices that are not 16-byte aligned are copied element
@@ -101,10 +105,12 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
   const int row0 = seq_q_start[seq] + seg_first;
   const int slot = seq_slot[seq];
   float* S_g = state + (((long long)slot * heads + head) * dk) * dv;
+  constexpr int PIECE = 16 / (int)sizeof(T);      // rows in a 16-byte piece of q or k
+  auto row_of = [&](int r) { return VEC ? ((r / PIECE) * ks + kr) * PIECE + (r % PIECE) : kr * ROWS + r; };
   float S[ROWS];
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
-    const int i = kr * ROWS + r;
+    const int i = row_of(r);
     S[r] = (live && i < dk && seg == 0) ? S_g[(long long)i * dv + col] : 0.0f;   // later stretches start from nothing
   }
   // a later stretch also leaves, per token, the product of the decays from its start (one thread group
@@ -173,27 +179,33 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
     // multiply-add per state element that carries the state on, and its reductions run side by side
     constexpr int GROUP = DECAY == DECAY_PER_CHANNEL ? 2 : 4;
     const int token_decay = DECAY == DECAY_PER_TOKEN;
-    const int at = valid > 0 ? kr * ROWS : 0;
+    const int at = VEC ? kr * PIECE : (valid > 0 ? kr * ROWS : 0);
     auto token = [&](int t) -> float {
       const T* w = raw + t * tok;
       const float vv = to_float(w[2 * dk + my_col]);
       float qq[ROWS], kk[ROWS], aa[ROWS];
-      load_rows<T, ROWS, VEC>(w + at, valid, qq);
-      load_rows<T, ROWS, VEC>(w + dk + at, valid, kk);
+      load_rows<T, ROWS, VEC>(w + at, valid, qq, ks * PIECE);
+      load_rows<T, ROWS, VEC>(w + dk + at, valid, kk, ks * PIECE);
       if (DECAY != DECAY_PER_HEAD) {
         if (token_decay) {
           const float a = dec[t];
 #pragma unroll
           for (int r = 0; r < ROWS; ++r) aa[r] = a;
+        } else if (VEC) {
+#pragma unroll
+          for (int r = 0; r < ROWS; r += 4) {      // a thread's rows come in runs of at least four
+            const float4 x = *reinterpret_cast<const float4*>(dec + t * dk + row_of(r));
+            aa[r] = x.x; aa[r + 1] = x.y; aa[r + 2] = x.z; aa[r + 3] = x.w;
+          }
         } else {
-          load_rows<float, ROWS, VEC>(dec + t * dk + at, valid, aa);
+          load_rows<float, ROWS, false>(dec + t * dk + at, valid, aa, 0);
         }
         if (keeps_cum) {
-          float* c_row = cum + (long long)(row0 + first + t) * ((long long)heads * dk) + head * dk + kr * ROWS;
+          float* c_row = cum + (long long)(row0 + first + t) * ((long long)heads * dk) + head * dk;
 #pragma unroll
           for (int r = 0; r < ROWS; ++r) {
             cp[r] *= aa[r];
-            if (r < valid) c_row[r] = cp[r];
+            if (r < valid) c_row[row_of(r)] = cp[r];
           }
         }
       }
@@ -229,15 +241,15 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
   if (n_segs > 1) {
     S_g = seg_state + ((((long long)seq * n_segs + seg) * heads + head) * dk) * dv;
     if (keeps_cum) {
-      float* d_row = seg_decay + (((long long)seq * n_segs + seg) * heads + head) * dk + kr * ROWS;
+      float* d_row = seg_decay + (((long long)seq * n_segs + seg) * heads + head) * dk;
 #pragma unroll
       for (int r = 0; r < ROWS; ++r)
-        if (r < valid) d_row[r] = cp[r];
+        if (r < valid) d_row[row_of(r)] = cp[r];
     }
   }
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
-    const int i = kr * ROWS + r;
+    const int i = row_of(r);
     if (live && i < dk) S_g[(long long)i * dv + col] = S[r];
   }
 }

@@ -60,15 +60,16 @@ __device__ __forceinline__ void load_rows(const T* p, int valid, float (&dst)[RO
 // 32 / ks value columns; a thread owns ROWS state rows of one column, so a token costs it ROWS
 // multiply-adds for the state, ROWS for the output, log2(ks) shuffles, and (VEC: rows and buffers
 // 16-byte aligned, the threads' rows cover the key size exactly) a few 16-byte loads of q and k from
-// shared memory.  Which rows: without VEC the neighbouring rows kr * ROWS ..; with VEC 16-byte pieces
-// dealt round-robin to the row groups (piece j of group kr covers rows (j * ks + kr) * PIECE ..), so
-// that the row groups of a warp read neighbouring pieces of a token's q and k and no two of them
-// meet in a shared-memory bank.
+// shared memory.  Which rows: the neighbouring rows kr * ROWS ..; or, with DEAL (VEC launches of steps
+// that bring some request more than four tokens), 16-byte pieces dealt round-robin to the row groups
+// (piece j of group kr covers rows (j * ks + kr) * PIECE ..), so that the row groups of a warp read
+// neighbouring pieces of a token's q and k and no two of them meet in a shared-memory bank.  (A step
+// of single tokens is bound by reading and writing the state and measured 2 % faster with neighbouring rows.)
 // Tokens come through shared memory a chunk at a time, SCAN_BUFFERS chunks deep: while the block walks
 // one chunk, the next ones' q, k, v (and decays) are on their way as 16-byte asynchronous copies, as
 // the projection left them (rows and head slices that are not 16-byte aligned are copied element
 // by element instead).  q_scale multiplies the output.
-template <typename T, int DECAY, int ROWS, bool VEC>
+template <typename T, int DECAY, int ROWS, bool VEC, bool DEAL>
 __global__ void __launch_bounds__(SCAN_THREADS)
 linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                              long long q_stride, long long k_stride, long long v_stride,
@@ -106,7 +107,7 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
   const int slot = seq_slot[seq];
   float* S_g = state + (((long long)slot * heads + head) * dk) * dv;
   constexpr int PIECE = 16 / (int)sizeof(T);      // rows in a 16-byte piece of q or k
-  auto row_of = [&](int r) { return VEC ? ((r / PIECE) * ks + kr) * PIECE + (r % PIECE) : kr * ROWS + r; };
+  auto row_of = [&](int r) { return DEAL ? ((r / PIECE) * ks + kr) * PIECE + (r % PIECE) : kr * ROWS + r; };
   float S[ROWS];
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
@@ -179,13 +180,14 @@ linear_attention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, c
     // multiply-add per state element that carries the state on, and its reductions run side by side
     constexpr int GROUP = DECAY == DECAY_PER_CHANNEL ? 2 : 4;
     const int token_decay = DECAY == DECAY_PER_TOKEN;
-    const int at = VEC ? kr * PIECE : (valid > 0 ? kr * ROWS : 0);
+    const int at = DEAL ? kr * PIECE : (valid > 0 ? kr * ROWS : 0);
+    const int piece_stride = DEAL ? ks * PIECE : PIECE;
     auto token = [&](int t) -> float {
       const T* w = raw + t * tok;
       const float vv = to_float(w[2 * dk + my_col]);
       float qq[ROWS], kk[ROWS], aa[ROWS];
-      load_rows<T, ROWS, VEC>(w + at, valid, qq, ks * PIECE);
-      load_rows<T, ROWS, VEC>(w + dk + at, valid, kk, ks * PIECE);
+      load_rows<T, ROWS, VEC>(w + at, valid, qq, piece_stride);
+      load_rows<T, ROWS, VEC>(w + dk + at, valid, kk, piece_stride);
       if (DECAY != DECAY_PER_HEAD) {
         if (token_decay) {
           const float a = dec[t];
@@ -369,13 +371,13 @@ scan_correct_kernel(const T* __restrict__ q, long long q_stride, const float* __
   }
 }
 
-template <typename T, int DECAY, int ROWS, bool VEC>
+template <typename T, int DECAY, int ROWS, bool VEC, bool DEAL>
 static int scan_launch(dim3 grid, size_t smem, cudaStream_t stream, const void* q, const void* k, const void* v,
                        long long q_stride, long long k_stride, long long v_stride, const float* decay, float* state,
                        float* out, const int32_t* seq_slot, const int32_t* seq_q_start, const int32_t* seq_q_len,
                        int heads, int dk, int dv, int ks, int chunk, int aligned, float q_scale, int seg_len, int n_segs,
                        int slices, float* seg_state, float* seg_decay, float* cum) {
-  auto kern = linear_attention_scan_kernel<T, DECAY, ROWS, VEC>;
+  auto kern = linear_attention_scan_kernel<T, DECAY, ROWS, VEC, DEAL>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return launch_status();
   launch_kernel(kern, grid, SCAN_THREADS, smem, stream, (const T*)q, (const T*)k, (const T*)v, q_stride, k_stride,
@@ -389,7 +391,7 @@ extern "C" int llm_linear_attention_scan(const void* q, const void* k, const voi
                                          float* state, float* out, const int32_t* seq_slot,
                                          const int32_t* seq_q_start, const int32_t* seq_q_len, int n_seqs, int heads,
                                          int dk, int dv, float q_scale, int seg_len, int n_segs, float* seg_state,
-                                         float* seg_decay, float* cum, cudaStream_t stream) {
+                                         float* seg_decay, float* cum, int max_q_len, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   LLM_HOST_CHECK(per_channel >= 0 && per_channel <= 2, ERR_BAD_SIZE);
   LLM_HOST_CHECK(n_segs >= 1 && (n_segs == 1 || (seg_len > 0 && seg_len % CORRECT_TOKENS == 0 && seg_state &&
@@ -420,11 +422,15 @@ extern "C" int llm_linear_attention_scan(const void* q, const void* k, const voi
   const bool vec = aligned && dk == ks * rows && ((2 * dk + cols_per_block) * esize) % 16 == 0;
 #define GO(T, DEC, ROWS)                                                                                        \
   do {                                                                                                          \
-    if (vec)                                                                                                    \
-      return scan_launch<T, DEC, ROWS, true>(grid, smem, stream, q, k, v, q_stride, k_stride, v_stride, decay,  \
+    if (vec && max_q_len > 4)                                                                                   \
+      return scan_launch<T, DEC, ROWS, true, true>(grid, smem, stream, q, k, v, q_stride, k_stride, v_stride, decay, \
                                              state, out, seq_slot, seq_q_start, seq_q_len, heads, dk, dv, ks,   \
                                              chunk, aligned, q_scale, seg_len, n_segs, slices, seg_state, seg_decay, cum); \
-    return scan_launch<T, DEC, ROWS, false>(grid, smem, stream, q, k, v, q_stride, k_stride, v_stride, decay,   \
+    if (vec)                                                                                                    \
+      return scan_launch<T, DEC, ROWS, true, false>(grid, smem, stream, q, k, v, q_stride, k_stride, v_stride, decay, \
+                                             state, out, seq_slot, seq_q_start, seq_q_len, heads, dk, dv, ks,   \
+                                             chunk, aligned, q_scale, seg_len, n_segs, slices, seg_state, seg_decay, cum); \
+    return scan_launch<T, DEC, ROWS, false, false>(grid, smem, stream, q, k, v, q_stride, k_stride, v_stride, decay, \
                                             state, out, seq_slot, seq_q_start, seq_q_len, heads, dk, dv, ks,    \
                                             chunk, aligned, q_scale, seg_len, n_segs, slices, seg_state, seg_decay, cum); \
   } while (0)

@@ -23,7 +23,7 @@ def lib():
     if _lib is None:
         l = build.load_library("linear_attention.cu")
         P, I, L, F = c_void_p, c_int, c_longlong, c_float
-        l.llm_linear_attention_scan.argtypes = [P, P, P, I, L, L, L, P, I, P, P, P, P, P, I, I, I, I, F, I, I, P, P, P, P]
+        l.llm_linear_attention_scan.argtypes = [P, P, P, I, L, L, L, P, I, P, P, P, P, P, I, I, I, I, F, I, I, P, P, P, I, P]
         l.llm_linear_attention_join.argtypes = [P, I, L, P, I, P, P, P, P, P, I, I, I, I, F, I, I, I, P, P, P, P]
         l.llm_decay_gate.argtypes = [P, I, L, P, P, P, I, I, I, F, P]
         l.llm_gated_group_norm.argtypes = [P, P, I, L, P, I, P, I, L, I, I, I, I, F, F, P]
@@ -88,7 +88,8 @@ def scan(ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Te
         q.data_ptr(), k.data_ptr(), v.data_ptr(), dtype_code(q.dtype), q.stride(0), k.stride(0), v.stride(0),
         decay.data_ptr(), mode, state.data_ptr(), out.data_ptr(),
         ctx.seq_slot.data_ptr(), ctx.seq_q_start.data_ptr(), ctx.seq_q_len.data_ptr(), ctx.n_seqs, heads, dk, dv,
-        float(q_scale), STRETCH, n_segs, seg_state, seg_decay, cum, ctx.stream), "linear_attention_scan")
+        float(q_scale), STRETCH, n_segs, seg_state, seg_decay, cum, int(ctx.max_q_len), ctx.stream),
+        "linear_attention_scan")
     if n_segs > 1:
         _check(lib().llm_linear_attention_join(
             q.data_ptr(), dtype_code(q.dtype), q.stride(0), decay.data_ptr(), 1 if per_channel else 0,

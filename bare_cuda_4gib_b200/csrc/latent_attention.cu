@@ -460,7 +460,8 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
   __nv_bfloat16* ps = ks + 2 * KB * ld;                               // [16][PLD]
   float* red = reinterpret_cast<float*>(ps + 16 * PLD);               // [2][4][16]: maxima, sums
   long long* koff = reinterpret_cast<long long*>(red + 128);          // [2][KB]: a key's place in the pool, -1: none
-  const int tile = blockIdx.x, t = tile / head_groups, hg = tile - t * head_groups, split = blockIdx.y;
+  // later tokens read more keys: they start first, so that the short ones fill the launch's tail
+  const int tile = gridDim.x - 1 - blockIdx.x, t = tile / head_groups, hg = tile - t * head_groups, split = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = positions[t], seq = row_seq[t];
   const int first = window > 0 ? max(0, pos - window + 1) : 0;
@@ -717,7 +718,8 @@ latent_attention_rows_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(lm_smem);      // [64][ld]: warp w's rows are 16 w ..
   __nv_bfloat16* ks = qs + 64 * ld;                                   // [2][KB][ld]
   long long* koff = reinterpret_cast<long long*>(ks + 2 * KB * ld);   // [3][KB]: the warps run up to a block apart
-  const int seq = blockIdx.x / tiles_per_seq, tok0 = (blockIdx.x - seq * tiles_per_seq) * 4, hg = blockIdx.y;
+  // a request's last tiles read the most keys: they start first, so that the short ones fill the launch's tail
+  const int seq = blockIdx.x / tiles_per_seq, tok0 = (tiles_per_seq - 1 - (blockIdx.x - seq * tiles_per_seq)) * 4, hg = blockIdx.y;
   const int q_len = seq_q_len[seq];
   if (tok0 >= q_len) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
